@@ -233,13 +233,35 @@ int ps_cuda_tp_import(ps_cuda_ctx *ctx, const void *handles, int n);
  *                f_i = rope_base^(-2 i / rope_dims); rope_factor > 0 adds YaRN: f_i <- f_i / factor * ramp_i +
  *                f_i (1 - ramp_i) with the ramp between the dims whose wavelength fits rope_original positions
  *                rope_fast and rope_slow times, and cos / sin scaled by 0.1 ln(factor) + 1.
+ *                chunk > 0: query i sees key j <= i only when floor(i / chunk) = floor(j / chunk) (chunks counted from position 0);
+ *                conv_taps > 1: a causal convolution over time on every channel of q, k and v directly after the projection
+ *                (y_t = sum_j w[c][j] u_(t - taps + 1 + j), zeros before position 0); the last conv_taps - 1 projected rows are
+ *                part of the sequence's state; qk_norm = PS_QKNORM_WHOLE: q (all heads at once) and k are RMS-normed as ONE
+ *                vector each with the weights q_norm / k_norm.
+ *   retention  - PS_MIXER_RETENTION: per head S_t = decay[h] S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, no soft-max; q and k
+ *                rotated (rotation below, rope_dims of qk_dim), k times qk_dim^(-1/2); every head's o divided by its root mean
+ *                square, the concatenation times silu(W_g h), then the output projection.  State: S [H][qk_dim][v_dim] fp32.
+ *   mamba2     - PS_MIXER_MAMBA2: W_in h = [z | x | B | C | dt] (inner = n_heads * v_dim, B and C of ssm_groups * ssm_state);
+ *                x|B|C through a causal convolution of conv_taps taps with bias and silu; dt = softplus(dt + dt_bias);
+ *                S_t = exp(-exp(A_log[h]) dt) S_(t-1) + dt B_t x_t^T, y_t = S_t^T C_t + D[h] x_t; y silu(z) is RMS-normed in
+ *                gate_norm_groups equal parts times mix_norm, then the output projection.  State: S [H][ssm_state][v_dim] fp32
+ *                and the last conv_taps - 1 inputs of the convolution.
+ *   recurrent state lives where a cache set keeps an attention layer's K rows (first buffer) and V^T rows (second buffer);
+ *                a sequence at position 0 starts from zero state whatever the buffers hold; ps_cuda_kv_rollback to a
+ *                position other than 0 is refused for models with such layers.
  *   dense ff   - PS_MLP_DENSE: one gated feed-forward of expert_ff rows with the expert's activation below.
  *   routed ff  - n_experts gated experts, the top_k largest router scores choose; router_act 1 = sigmoid scores;
  *                route_on_input = 1: the score multiplies the expert's INPUT; route_renorm = 1: the chosen scores are
- *                divided by their sum.  Expert: g = min(Wg z, act_limit), u = clamp(Wu z, +-act_limit),
- *                y = g * sigmoid(act_alpha * g) * (u + up_shift), out = Wd y.
+ *                divided by their sum (+ route_renorm_eps); router_act 2 = soft-max over all experts; route_groups > 1:
+ *                the experts form that many equal groups of neighbours, a group is worth its best score and only the
+ *                route_keep best groups can be chosen from.  Expert: g = min(Wg z, act_limit), u = clamp(Wu z, +-act_limit),
+ *                y = g * sigmoid(act_alpha * g) * (u + up_shift), out = Wd y; act_kind PS_ACT_GELU_TANH: y = gelu_tanh(Wg z) * (Wu z).
+ *                shared_ff > 0: one more expert of that many rows runs for every token and is added, times
+ *                sigmoid(shared_sg . z) when shared_gate = 1.
+ *   raw_input  - sequential blocks: the sublayers read the residual stream itself (no norm on the way in).
  *   norm       - RMS norm with eps inside the root; norm_unit_offset = 1: the stored weight is around zero (1 + w);
- *                norm_groups > 1: the vector is cut into that many equal parts, each divided by its own root mean square.
+ *                norm_groups > 1: the vector is cut into that many equal parts, each divided by its own root mean square;
+ *                norm_scalar = 1: every norm's weight is a single number for all coordinates.
  * The context made by ps_cuda_create_arch is an ordinary ps_cuda_ctx: ps_cuda_forward, ps_cuda_decode_greedy,
  * ps_cuda_sample_topk, ps_cuda_logits_dev, the ps_cuda_kv_* position calls and the ps_cuda_session_* calls work on it
  * as on a llama context (the per-layer cache rows have the layer's own widths; V is kept transposed like there).  The
@@ -248,11 +270,14 @@ int ps_cuda_tp_import(ps_cuda_ctx *ctx, const void *handles, int n);
  * compute = PS_COMPUTE_BF16: matrix products take bfloat16 operands and accumulate in fp32; the residual stream, norms,
  * attention scores / weights, routers and the cache stay fp32.  PS_COMPUTE_F32: every product in true fp32 (FMA). */
 enum ps_cuda_compute { PS_COMPUTE_BF16 = 0, PS_COMPUTE_F32 = 1 };
-enum ps_cuda_mixer_kind { PS_MIXER_ATTENTION = 1, PS_MIXER_LATENT = 2 };
+enum ps_cuda_mixer_kind { PS_MIXER_ATTENTION = 1, PS_MIXER_LATENT = 2, PS_MIXER_RETENTION = 3, PS_MIXER_MAMBA2 = 4 };
 enum ps_cuda_mlp_kind { PS_MLP_NONE = 0, PS_MLP_ROUTED = 1, PS_MLP_DENSE = 2 };
 enum ps_cuda_block_kind { PS_BLOCK_PARALLEL = 0, PS_BLOCK_SEQUENTIAL = 1 };
 enum ps_cuda_sink_kind { PS_SINK_NONE = 0, PS_SINK_ZERO = 1, PS_SINK_LEARNED = 2 };
 enum ps_cuda_vmix_kind { PS_VMIX_NONE = 0, PS_VMIX_SOURCE = 1, PS_VMIX_BLEND = 2 };
+enum ps_cuda_qknorm_kind { PS_QKNORM_NONE = 0, PS_QKNORM_HEAD = 1, PS_QKNORM_WHOLE = 2 };
+enum ps_cuda_act_kind { PS_ACT_SWISH = 0, PS_ACT_GELU_TANH = 1 };
+enum ps_cuda_router_act { PS_ROUTER_SIGMOID = 1, PS_ROUTER_SOFTMAX = 2 };
 
 typedef struct {
     int32_t mixer_kind;
@@ -265,18 +290,27 @@ typedef struct {
     int32_t sink;                       /* enum ps_cuda_sink_kind: one more term in the soft-max denominator */
     int32_t mlp_kind;
     int32_t n_experts, top_k, expert_ff;
-    int32_t router_act;                 /* 1 = sigmoid */
+    int32_t router_act;                 /* enum ps_cuda_router_act */
     int32_t route_on_input, route_renorm;
     float   act_limit, act_alpha, up_shift;
     int32_t block_kind;                 /* enum ps_cuda_block_kind */
     int32_t post_norm;                  /* sequential blocks: every sublayer's output is normed before the residual add */
-    int32_t qk_norm;                    /* q and k divided by their root mean square per head */
+    int32_t qk_norm;                    /* enum ps_cuda_qknorm_kind */
     int32_t window;                     /* > 0: keys further back than window - 1 positions are not seen */
     int32_t log_bias;                   /* score -= r1[h] * ln(1 + r2[h] * distance) */
     int32_t v_mix;                      /* enum ps_cuda_vmix_kind */
     int32_t q_rank, kv_rank, rot_dim;   /* latent attention */
     int32_t rope_dims, rope_original;   /* rotation: rotated dims; YaRN's original context */
     float   rope_base, rope_factor, rope_fast, rope_slow; /* rope_factor = 0: plain rotation */
+    int32_t raw_input;                  /* sequential blocks: no norm on a sublayer's input */
+    int32_t chunk;                      /* > 0: attention inside chunks of this many positions only */
+    int32_t conv_taps;                  /* short causal convolution: on q, k, v (attention), on x|B|C (mamba2); 0 or 1 = none */
+    int32_t ssm_state, ssm_groups;      /* mamba2: state size N, groups of heads that share B and C */
+    int32_t gate_norm_groups;           /* mamba2: parts of the gated output that are normed separately */
+    int32_t act_kind;                   /* enum ps_cuda_act_kind */
+    int32_t route_groups, route_keep;   /* group-limited routing (route_groups <= 1: every expert can be chosen) */
+    float   route_renorm_eps;           /* added to the sum of the chosen scores before the division */
+    int32_t shared_ff, shared_gate;     /* rows of the shared expert (0 = none); 1 = its output is scaled by sigmoid(shared_sg . z) */
 } ps_cuda_layer_desc;
 
 typedef struct {
@@ -287,6 +321,7 @@ typedef struct {
     int32_t compute;                    /* enum ps_cuda_compute */
     const ps_cuda_layer_desc *layers;   /* n_layers entries */
     int32_t norm_groups;                /* 0 or 1: one group */
+    int32_t norm_scalar;                /* the norms' weights are single numbers */
 } ps_cuda_arch_desc;
 
 /* matrices [out][in] in bfloat16; vectors and the small tables in bfloat16 or fp32 */
@@ -297,6 +332,10 @@ typedef struct {
     ps_cuda_tensor norm_mix_out, norm_ff, norm_ff_out;
     ps_cuda_tensor r1, r2, sink, vmix;  /* [H], [H], [H], scalar */
     ps_cuda_tensor dq, dq_norm, uq, dkv, dkv_norm, uk, uv; /* latent attention */
+    ps_cuda_tensor q_norm, k_norm, q_conv, k_conv, v_conv; /* whole-projection norms [H * qk_dim], [G * qk_dim]; convolutions [channels][taps] */
+    ps_cuda_tensor g, decay;            /* retention: gate projection [H * v_dim][dim]; decays [H] */
+    ps_cuda_tensor w_in, conv_w, conv_b, dt_bias, a_log, d_skip, mix_norm; /* mamba2 */
+    ps_cuda_tensor shared_gate, shared_up, shared_down, shared_sg; /* shared expert */
 } ps_cuda_arch_layer_weights;
 
 typedef struct {

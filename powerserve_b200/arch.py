@@ -16,6 +16,8 @@ import json
 import os
 from typing import Callable, Dict, List, Optional, Tuple
 
+import numpy as np
+
 from . import capi, safetensors
 from .capi import ArchDesc, ArchLayerWeights, ArchWeights, LayerDesc, Tensor
 
@@ -31,26 +33,30 @@ class LayerListModel(capi.CudaModel):
             raise capi.PsCudaError(f"{path}: unknown architecture {name!r} (known: {sorted(ARCHITECTURES)})")
         describe, tensor_names = ARCHITECTURES[name]
         self.cfg = cfg
+        self._keep: List[object] = []
         self._file = safetensors.SafeTensorsFile(os.path.join(path, "model.safetensors"))
         self.tensors = self._file.tensors
         compute = {"bfloat16": capi.COMPUTE_BF16, "float32": capi.COMPUTE_F32}[dtype]
         layers, top = describe(cfg, self.tensors)
         self._layer_descs = (LayerDesc * len(layers))(*layers)
         self.desc = ArchDesc(top["dim"], top["vocab_size"], len(layers), int(n_ctx), int(max_batch), top["norm_eps"], top["embed_scale"],
-                             top["norm_unit_offset"], compute, self._layer_descs, int(top.get("norm_groups", 1)))
+                             top["norm_unit_offset"], compute, self._layer_descs, int(top.get("norm_groups", 1)), int(top.get("norm_scalar", 0)))
         self.vocab = self.desc.vocab_size
         self.be = capi.CudaBackend(self.desc, device)
 
-        def T(n: Optional[str]) -> Tensor:
+        def T(n) -> Tensor:
             if n is None:
                 return Tensor(None, 0, 0)
+            if not isinstance(n, str):          # constants of the configuration, handed over as a float32 array
+                arr = np.ascontiguousarray(n, np.float32)
+                self._keep.append(arr)
+                return Tensor(arr.ctypes.data, safetensors.PS_F32, 0)
             if n not in self.tensors:
                 raise capi.PsCudaError(f"{path}: tensor {n} is missing")
             t = self.tensors[n]
             return Tensor(t.host_ptr, t.ps_type, 0)
 
         names = tensor_names(cfg)
-        self._keep: List[object] = []
         self._lw = (ArchLayerWeights * len(layers))()
         for i, ln in enumerate(names["layers"]):
             lw = ArchLayerWeights()
@@ -201,7 +207,101 @@ def _vanapel_tensor_names(cfg: dict) -> dict:
     return out
 
 
+# ------------------------------------------------------------------------------------------------------------ Dozotar
+# Decoder-only; every layer is a sequential block whose sublayers read the residual stream itself and are normed on the way out only,
+#   x <- x + N(mixer(x)) g1,  x <- x + N(ff(x)) g2,   N an RMS norm, g1 / g2 single numbers.  Three mixers, chosen per layer by "type":
+#   "attention"  grouped-query, no rotation; a short causal convolution on q, k and v after the projections; q and k normed over the
+#                whole projection with weights; a bucketed distance bias; attention inside chunks of mask.size positions; plain soft-max.
+#   "retention"  linear attention with a fixed decay per head: rotated q / k (rotate-half pairs), k / sqrt(dim), per-head RMS of the
+#                output, a silu gate.
+#   "mamba2"     state-space recurrence: one input projection [z | x | B | C | dt], convolution + silu on x|B|C, softplus step sizes,
+#                gated output normed in norm_groups parts.
+# Feed-forward: dense with the tanh form of gelu, or soft-max-routed silu experts chosen inside the best groups of neighbours, weights
+# renormalised (+ 1e-20), plus a shared expert behind a sigmoid gate.
+def _dozotar_describe(cfg: dict, tensors) -> Tuple[List[LayerDesc], dict]:
+    layers = []
+    for i, l in enumerate(cfg["layers"]):
+        m = l["mixer"]
+        d = LayerDesc()
+        d.block_kind, d.post_norm, d.raw_input = capi.BLOCK_SEQUENTIAL, 1, 1
+        d.n_heads, d.v_dim = m["heads"], m["vdim"]
+        if l["type"] == "attention":
+            d.mixer_kind = capi.MIXER_ATTENTION
+            d.n_kv_heads, d.qk_dim = m["kv_heads"], m["dim"]
+            d.score_scale = m["scale"]
+            d.qk_norm = capi.QKNORM_WHOLE
+            d.conv_taps = int(m.get("conv") or 0)
+            d.rel_buckets = int(tensors[f"l{i}.mix.rel"].shape[0])      # the table's own row count
+            d.rel_max_dist = m["bias_max"]
+            d.chunk = int((m.get("mask") or {}).get("size", 0))
+        elif l["type"] == "retention":
+            d.mixer_kind = capi.MIXER_RETENTION
+            d.n_kv_heads, d.qk_dim = m["heads"], m["dim"]
+            rot = m.get("rot") or {}
+            d.rope_dims, d.rope_base = int(rot.get("dims", 0)), float(rot.get("base", 10000.0))
+            if len(m["decay"]) != m["heads"]:
+                raise capi.PsCudaError(f"Dozotar layer {i}: {len(m['decay'])} decays for {m['heads']} heads")
+        elif l["type"] == "mamba2":
+            d.mixer_kind = capi.MIXER_MAMBA2
+            d.n_kv_heads = m["groups"]
+            d.ssm_state, d.ssm_groups, d.gate_norm_groups = m["state"], m["groups"], m["norm_groups"]
+            d.conv_taps = int(tensors[f"l{i}.mix.conv"].shape[1])      # the taps the stored kernel has
+        else:
+            raise capi.PsCudaError(f"Dozotar layer {i}: unknown mixer type {l['type']!r}")
+        mlp = l.get("mlp")
+        d.act_limit, d.act_alpha, d.up_shift = float("inf"), 1.0, 0.0   # silu(gate) * up where the activation is the swish kind
+        if mlp is None:
+            d.mlp_kind = capi.MLP_NONE
+        elif mlp.get("kind") == "dense":
+            d.mlp_kind, d.expert_ff, d.act_kind = capi.MLP_DENSE, mlp["ff"], capi.ACT_GELU_TANH
+        elif mlp.get("kind") == "moe":
+            r = mlp["router"]
+            d.mlp_kind, d.act_kind = capi.MLP_ROUTED, capi.ACT_SWISH
+            d.n_experts, d.top_k, d.expert_ff = r["experts"], r["top"], mlp["expert"]["ff"]
+            d.router_act, d.route_on_input, d.route_renorm, d.route_renorm_eps = capi.ROUTER_SOFTMAX, 0, 1, 1e-20
+            g = r.get("groups") or {}
+            d.route_groups, d.route_keep = int(g.get("count", 1)), int(g.get("keep", 1))
+            if mlp.get("shared"):
+                d.shared_ff, d.shared_gate = mlp["shared"]["ff"], 1
+        else:
+            raise capi.PsCudaError(f"Dozotar layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+        layers.append(d)
+    top = {"dim": cfg["width"], "vocab_size": cfg["vocab"], "norm_eps": cfg["norm"]["eps"], "embed_scale": 1.0, "norm_unit_offset": 0, "norm_scalar": 1}
+    return layers, top
+
+
+def _dozotar_tensor_names(cfg: dict) -> dict:
+    out = {"embed": "embed", "final_norm": "final.norm", "head": "head", "layers": []}
+    for i, l in enumerate(cfg["layers"]):
+        p = f"l{i}."
+        n = {"norm_mix_out": p + "norm1", "o": p + "mix.o"}
+        if l["type"] == "attention":
+            n.update({"q": p + "mix.q", "k": p + "mix.k", "v": p + "mix.v", "q_norm": p + "mix.q.norm", "k_norm": p + "mix.k.norm", "rel": p + "mix.rel"})
+            if l["mixer"].get("conv"):
+                n.update({"q_conv": p + "mix.q.conv", "k_conv": p + "mix.k.conv", "v_conv": p + "mix.v.conv"})
+        elif l["type"] == "retention":
+            n.update({"q": p + "mix.q", "k": p + "mix.k", "v": p + "mix.v", "g": p + "mix.g", "decay": np.asarray(l["mixer"]["decay"], np.float32)})
+        else:
+            n.update({"w_in": p + "mix.in", "conv_w": p + "mix.conv", "conv_b": p + "mix.conv.b", "dt_bias": p + "mix.dt_bias", "a_log": p + "mix.A_log",
+                      "d_skip": p + "mix.D", "mix_norm": p + "mix.norm"})
+        mlp = l.get("mlp")
+        if mlp is not None:
+            n["norm_ff_out"] = p + "norm2"
+            if mlp.get("kind") == "moe":
+                n["router"] = p + "mlp.router"
+                for f in ("gate", "up", "down"):
+                    n[f] = [f"{p}mlp.e{e}.{f}" for e in range(mlp["router"]["experts"])]
+                if mlp.get("shared"):
+                    n.update({"shared_gate": p + "mlp.shared.gate", "shared_up": p + "mlp.shared.up", "shared_down": p + "mlp.shared.down", "shared_sg": p + "mlp.shared.sg"})
+            else:
+                for f in ("gate", "up", "down"):
+                    n[f] = [f"{p}mlp.{f}"]
+        out["layers"].append(n)
+    return out
+
+
 ARCHITECTURES: Dict[str, Tuple[Callable, Callable]] = {
+    "Dozotar": (_dozotar_describe, _dozotar_tensor_names),
     "Nufusun": (_nufusun_describe, _nufusun_tensor_names),
     "Vanapel": (_vanapel_describe, _vanapel_tensor_names),
 }

@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libps_cuda.so")
 SOURCES = ["ps_cuda.cu", "ps_arch.cu"]
 HEADERS = ["ps_step.cuh", "ps_tc.cuh", "ps_rw.cuh", "ps_decode.cuh", "ps_kernels.cuh", "ps_math.cuh", "ps_mv32.cuh", "ps_ptx.cuh", "ps_arch.h", "ps_arch_kernels.cuh",
-           "ps_arch_decode.cuh", "ps_arch_tc.cuh",
+           "ps_arch_decode.cuh", "ps_arch_tc.cuh", "ps_arch_recur.cuh",
            os.path.join("..", "..", "include", "ps_cuda.h")]
 
 COMMON_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-cudart", "shared"]
@@ -46,7 +46,7 @@ def _unit_stale(src: str) -> bool:
     if not os.path.exists(o):
         return True
     t = os.path.getmtime(o)
-    mine = {"ps_arch.cu": ["ps_arch.h", "ps_arch_kernels.cuh", "ps_arch_decode.cuh", "ps_arch_tc.cuh", "ps_ptx.cuh", os.path.join("..", "..", "include", "ps_cuda.h")]}.get(src, HEADERS)
+    mine = {"ps_arch.cu": ["ps_arch.h", "ps_arch_kernels.cuh", "ps_arch_decode.cuh", "ps_arch_tc.cuh", "ps_arch_recur.cuh", "ps_ptx.cuh", os.path.join("..", "..", "include", "ps_cuda.h")]}.get(src, HEADERS)
     deps = [os.path.join(CSRC, f) for f in [src] + mine] + [os.path.abspath(__file__)]
     return any(os.path.getmtime(os.path.normpath(d)) > t for d in deps if os.path.exists(os.path.normpath(d)))
 

@@ -52,17 +52,22 @@ class LayerDesc(C.Structure):
                 ("act_limit", C.c_float), ("act_alpha", C.c_float), ("up_shift", C.c_float),
                 ("block_kind", C.c_int32), ("post_norm", C.c_int32), ("qk_norm", C.c_int32), ("window", C.c_int32), ("log_bias", C.c_int32),
                 ("v_mix", C.c_int32), ("q_rank", C.c_int32), ("kv_rank", C.c_int32), ("rot_dim", C.c_int32), ("rope_dims", C.c_int32),
-                ("rope_original", C.c_int32), ("rope_base", C.c_float), ("rope_factor", C.c_float), ("rope_fast", C.c_float), ("rope_slow", C.c_float)]
+                ("rope_original", C.c_int32), ("rope_base", C.c_float), ("rope_factor", C.c_float), ("rope_fast", C.c_float), ("rope_slow", C.c_float),
+                ("raw_input", C.c_int32), ("chunk", C.c_int32), ("conv_taps", C.c_int32), ("ssm_state", C.c_int32), ("ssm_groups", C.c_int32),
+                ("gate_norm_groups", C.c_int32), ("act_kind", C.c_int32), ("route_groups", C.c_int32), ("route_keep", C.c_int32),
+                ("route_renorm_eps", C.c_float), ("shared_ff", C.c_int32), ("shared_gate", C.c_int32)]
 
 
 class ArchDesc(C.Structure):
     _fields_ = [("dim", C.c_int32), ("vocab_size", C.c_int32), ("n_layers", C.c_int32), ("n_ctx", C.c_int32), ("max_batch", C.c_int32),
                 ("norm_eps", C.c_float), ("embed_scale", C.c_float), ("norm_unit_offset", C.c_int32), ("compute", C.c_int32),
-                ("layers", C.POINTER(LayerDesc)), ("norm_groups", C.c_int32)]
+                ("layers", C.POINTER(LayerDesc)), ("norm_groups", C.c_int32), ("norm_scalar", C.c_int32)]
 
 
 # the layer tensors after the expert lists, in the order of ps_cuda_arch_layer_weights
-ARCH_LAYER_VECTORS_2 = ("norm_mix_out", "norm_ff", "norm_ff_out", "r1", "r2", "sink", "vmix", "dq", "dq_norm", "uq", "dkv", "dkv_norm", "uk", "uv")
+ARCH_LAYER_VECTORS_2 = ("norm_mix_out", "norm_ff", "norm_ff_out", "r1", "r2", "sink", "vmix", "dq", "dq_norm", "uq", "dkv", "dkv_norm", "uk", "uv",
+                        "q_norm", "k_norm", "q_conv", "k_conv", "v_conv", "g", "decay", "w_in", "conv_w", "conv_b", "dt_bias", "a_log", "d_skip", "mix_norm",
+                        "shared_gate", "shared_up", "shared_down", "shared_sg")
 
 
 class ArchLayerWeights(C.Structure):
@@ -81,6 +86,10 @@ MIXER_LATENT, MLP_DENSE = 2, 2
 BLOCK_PARALLEL, BLOCK_SEQUENTIAL = 0, 1
 SINK_NONE, SINK_ZERO, SINK_LEARNED = 0, 1, 2
 VMIX_NONE, VMIX_SOURCE, VMIX_BLEND = 0, 1, 2
+MIXER_RETENTION, MIXER_MAMBA2 = 3, 4
+QKNORM_NONE, QKNORM_HEAD, QKNORM_WHOLE = 0, 1, 2
+ACT_SWISH, ACT_GELU_TANH = 0, 1
+ROUTER_SIGMOID, ROUTER_SOFTMAX = 1, 2
 
 _lib: Optional[C.CDLL] = None
 

@@ -21,6 +21,7 @@ typedef __nv_bfloat16 bf16;
 
 #include "ps_arch_kernels.cuh"
 #include "ps_arch_decode.cuh"
+#include "ps_arch_recur.cuh"
 #include "ps_arch_tc.cuh"
 
 // ====================================================================================================================== host
@@ -44,7 +45,21 @@ struct PsArchLayer {
     double *rope_freq = nullptr;
     float rope_mscale = 1.0f;
     uint8_t *t_uq = nullptr;
+    // generic sequential layers (raw input, recurrent mixers, short convolutions, routed experts in a sequential block)
+    bool gen2 = false;
+    int64_t k_floats = 0, v_floats = 0; // floats of the layer's two buffers in a cache set when they are not plain K rows / V^T rows
+    float *conv_w = nullptr, *conv_b = nullptr; // short convolution [channels][taps] (attention: q | k | v channels), bias
+    int conv_c = 0;                            // channels through the convolution
+    float *q_norm = nullptr, *k_norm = nullptr, *decay = nullptr, *dt_bias = nullptr, *a_log = nullptr, *d_skip = nullptr, *mix_norm = nullptr;
+    bf16 *wsg = nullptr, *wsu = nullptr, *wsd = nullptr; // shared expert
+    uint8_t *t_sg = nullptr, *t_su = nullptr, *t_sd = nullptr;
 };
+
+static inline PaAct pa_act_of(const ps_cuda_layer_desc &l) { return PaAct{l.act_limit, l.act_alpha, l.up_shift, l.act_kind}; }
+static inline PaRoute pa_route_of(const ps_cuda_layer_desc &l) {
+    return PaRoute{l.n_experts, l.top_k, l.router_act, l.route_groups, l.route_keep, l.route_renorm, l.route_renorm_eps, l.shared_ff > 0 && l.shared_gate};
+}
+static inline bool pa_recurrent(const ps_cuda_layer_desc &l) { return l.mixer_kind == PS_MIXER_RETENTION || l.mixer_kind == PS_MIXER_MAMBA2; }
 
 struct PsArch {
     ps_cuda_arch_desc d{};
@@ -62,6 +77,9 @@ struct PsArch {
     float *cq = nullptr, *lq = nullptr, *qa = nullptr, *att2 = nullptr; // latent attention: normed query latent, queries, queries with W_uk folded in, values after W_uv
     float *vsrc = nullptr; // value rows of the tokens in flight from the layer others blend theirs with
     float *x2 = nullptr;   // second residual buffer of the single-token step of sequential blocks
+    float *cv = nullptr, *sh = nullptr, *ffo = nullptr, *sgate = nullptr; // convolution output; shared expert's output; summed feed-forward output; shared gate per token
+    int max_cv = 0;
+    bool has_state = false; // some layer carries state that cannot be cut back (recurrences, convolution tails)
     int max_rq = 0, max_lq = 0, max_qa = 0, max_att2 = 0, vsrc_w = 0;
     int ldP = 0;
     int64_t ldS = 0;
@@ -255,35 +273,71 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
         PsArchLayer &w = a->L[(size_t)i];
         w.d = l;
         (l.block_kind == PS_BLOCK_SEQUENTIAL ? a->has_seq : a->has_par) = true;
-        if (l.mixer_kind != PS_MIXER_ATTENTION && l.mixer_kind != PS_MIXER_LATENT) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unknown mixer kind %d", i, l.mixer_kind));
-        const bool latent = l.mixer_kind == PS_MIXER_LATENT;
+        if (l.mixer_kind < PS_MIXER_ATTENTION || l.mixer_kind > PS_MIXER_MAMBA2) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unknown mixer kind %d", i, l.mixer_kind));
+        const bool latent = l.mixer_kind == PS_MIXER_LATENT, recur = pa_recurrent(l);
+        w.gen2 = l.block_kind == PS_BLOCK_SEQUENTIAL && (l.raw_input || recur || l.conv_taps > 1 || l.qk_norm == PS_QKNORM_WHOLE || l.chunk > 0 || l.mlp_kind == PS_MLP_ROUTED ||
+                                                         l.rel_buckets > 0 || l.act_kind != PS_ACT_SWISH || l.shared_ff > 0);
+        if (!w.gen2 && (l.raw_input || recur || l.conv_taps > 1 || l.qk_norm == PS_QKNORM_WHOLE || l.chunk > 0 || l.act_kind != PS_ACT_SWISH || l.shared_ff > 0 ||
+                        l.router_act == PS_ROUTER_SOFTMAX || l.route_groups > 1))
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: raw sublayer inputs, recurrent mixers, convolutions, whole-projection norms, chunked masks, gelu, soft-max / grouped routers and shared experts need a sequential block", i));
+        if (w.gen2 && (latent || l.v_mix || l.qk_norm == PS_QKNORM_HEAD || l.proj_bias || l.head_mix || l.head_temp))
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: latent attention, value blending, per-head unit norms, projection biases and head mixing are not combined with this layer's other mechanisms", i));
+        if (w.gen2 && l.mlp_kind == PS_MLP_ROUTED && !l.raw_input && d.norm_groups > 1)
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: routed experts behind a group norm", i));
+        if (l.chunk < 0 || l.conv_taps < 0 || l.conv_taps > 16 || l.act_kind < PS_ACT_SWISH || l.act_kind > PS_ACT_GELU_TANH || l.shared_ff < 0)
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: chunk %d, %d convolution taps, activation %d, shared expert of %d rows", i, l.chunk, l.conv_taps, l.act_kind, l.shared_ff));
+        if (l.mixer_kind == PS_MIXER_RETENTION && (l.rope_dims < 0 || l.rope_dims > l.qk_dim || (l.rope_dims & 1) || (l.rope_dims > 0 && !(l.rope_base > 0.f)) || l.qk_dim > 256 || l.rope_factor != 0.f))
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: retention with heads of %d of which %d rotate (at most 256)", i, l.qk_dim, l.rope_dims));
+        if (l.mixer_kind == PS_MIXER_MAMBA2 && (l.ssm_state <= 0 || l.ssm_state > 256 || l.ssm_groups <= 0 || l.n_heads % std::max(l.ssm_groups, 1) || l.gate_norm_groups <= 0 ||
+                                                (l.n_heads * l.v_dim) % std::max(l.gate_norm_groups, 1) || l.conv_taps < 1))
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: state-space mixer with state %d, %d groups, %d norm parts, %d taps", i, l.ssm_state, l.ssm_groups, l.gate_norm_groups, l.conv_taps));
         if (latent && (l.q_rank <= 0 || l.kv_rank <= 0 || l.rot_dim < 0 || l.rope_dims < 0 || l.rope_dims > l.rot_dim || (l.rope_dims & 1) || (l.rope_dims > 0 && !(l.rope_base > 0.f)) ||
                        l.n_kv_heads != 1 || l.proj_bias || l.head_temp || l.head_mix || l.rel_buckets || l.qk_norm || l.v_mix || l.block_kind != PS_BLOCK_SEQUENTIAL))
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unsupported latent attention (ranks %d / %d, %d rotated dims of which %d rotate)", i, l.q_rank, l.kv_rank, l.rot_dim, l.rope_dims));
         if (l.block_kind != PS_BLOCK_PARALLEL && l.block_kind != PS_BLOCK_SEQUENTIAL) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unknown block kind %d", i, l.block_kind));
         if (l.block_kind == PS_BLOCK_PARALLEL && (l.post_norm || l.qk_norm || l.v_mix || l.mlp_kind == PS_MLP_DENSE))
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: output norms, unit-RMS q / k, value blending and the dense feed-forward need a sequential block", i));
-        if (l.block_kind == PS_BLOCK_SEQUENTIAL && (l.mlp_kind == PS_MLP_ROUTED || l.proj_bias || l.head_mix || l.head_temp || l.rel_buckets))
+        if (l.block_kind == PS_BLOCK_SEQUENTIAL && !w.gen2 && (l.mlp_kind == PS_MLP_ROUTED || l.proj_bias || l.head_mix || l.head_temp || l.rel_buckets))
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: routed experts, projection biases, head mixing / temperatures and the bias table need a parallel block", i));
         if (l.window < 0 || l.sink < PS_SINK_NONE || l.sink > PS_SINK_LEARNED || l.v_mix < PS_VMIX_NONE || l.v_mix > PS_VMIX_BLEND)
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: window %d, sink kind %d, value blending %d", i, l.window, l.sink, l.v_mix));
-        if (l.n_heads <= 0 || l.n_kv_heads <= 0 || l.n_heads % l.n_kv_heads || l.qk_dim <= 0 || l.v_dim <= 0 || l.n_heads > PA_MAX_HEADS)
+        if (l.n_heads <= 0 || l.v_dim <= 0 || (!recur && l.n_heads > PA_MAX_HEADS) ||
+            (l.mixer_kind != PS_MIXER_MAMBA2 && (l.qk_dim <= 0 || (!recur && (l.n_kv_heads <= 0 || l.n_heads % l.n_kv_heads)))))
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unsupported head geometry (%d / %d heads, sizes %d / %d; at most %d heads)", i, l.n_heads,
                               l.n_kv_heads, l.qk_dim, l.v_dim, PA_MAX_HEADS));
         if (l.rel_buckets < 0 || l.rel_buckets > 65535 || (l.rel_buckets > 0 && (l.rel_buckets < 2 || !(l.rel_max_dist > (float)(l.rel_buckets / 2)))))
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: distance-bias table of %d rows up to distance %g", i, l.rel_buckets, (double)l.rel_max_dist));
         if (l.mlp_kind != PS_MLP_NONE && l.mlp_kind != PS_MLP_ROUTED && l.mlp_kind != PS_MLP_DENSE) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unknown feed-forward kind %d", i, l.mlp_kind));
-        if (l.mlp_kind == PS_MLP_ROUTED && (l.n_experts <= 0 || l.n_experts > PA_MAX_EXPERTS || l.top_k <= 0 || l.top_k > l.n_experts || l.expert_ff <= 0 || l.router_act != 1))
+        if (l.mlp_kind == PS_MLP_ROUTED && (l.n_experts <= 0 || l.n_experts > PA_MAX_EXPERTS || l.top_k <= 0 || l.top_k > l.n_experts || l.expert_ff <= 0 ||
+                                         (l.router_act != PS_ROUTER_SIGMOID && l.router_act != PS_ROUTER_SOFTMAX) ||
+                                         (l.route_groups > 1 && (l.n_experts % l.route_groups || l.route_keep <= 0 || l.route_keep > l.route_groups || l.top_k > l.route_keep * (l.n_experts / l.route_groups)))))
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unsupported routed feed-forward (%d experts, top %d, ff %d, router activation %d)", i, l.n_experts,
                               l.top_k, l.expert_ff, l.router_act));
         if (l.mlp_kind == PS_MLP_DENSE && l.expert_ff <= 0) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: dense feed-forward of %d rows", i, l.expert_ff));
         // the attention kernels see a latent layer as one shared key head of kv_rank + rot_dim dims whose values are the latents
         const int a_dq = latent ? l.kv_rank + l.rot_dim : l.qk_dim, a_dv = latent ? l.kv_rank : l.v_dim;
-        if (pa_dec_scores_smem(l.n_heads, l.n_kv_heads, a_dq) > 160 * 1024 || (size_t)d.dim * 4 > 160 * 1024)
+        if ((!recur && pa_dec_scores_smem(l.n_heads, l.n_kv_heads, a_dq) > 160 * 1024) || (size_t)d.dim * 4 > 160 * 1024)
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: %d heads of size %d (or width %d) exceed the single-token kernels' shared memory", i, l.n_heads, a_dq, d.dim));
         w.qd = l.n_heads * a_dq; w.kd = l.n_kv_heads * a_dq; w.vd = l.n_kv_heads * a_dv; w.od = l.n_heads * l.v_dim;
         w.pw = latent ? l.q_rank + l.kv_rank + l.rot_dim : w.qd + w.kd + w.vd;
         w.aw = l.n_heads * a_dv;
+        if (l.mixer_kind == PS_MIXER_RETENTION) { // q | k | v | gate; the state S [H][qk_dim][v_dim] takes the place of the K rows
+            w.qd = w.kd = l.n_heads * l.qk_dim; w.vd = w.od = w.aw = l.n_heads * l.v_dim;
+            w.pw = 2 * w.qd + 2 * w.od;
+            w.k_floats = (int64_t)l.n_heads * l.qk_dim * l.v_dim; w.v_floats = 4;
+        } else if (l.mixer_kind == PS_MIXER_MAMBA2) { // z | x | B | C | dt; S [H][state][v_dim], and the convolution's tail in the second buffer
+            const int inner = l.n_heads * l.v_dim, gn = l.ssm_groups * l.ssm_state;
+            w.qd = w.kd = gn; w.vd = w.od = w.aw = inner;
+            w.pw = 2 * inner + 2 * gn + l.n_heads;
+            w.conv_c = inner + 2 * gn;
+            w.k_floats = (int64_t)l.n_heads * l.ssm_state * l.v_dim; w.v_floats = std::max<int64_t>(4, (int64_t)(l.conv_taps - 1) * w.conv_c);
+        } else if (w.gen2 && l.conv_taps > 1) { // the last taps - 1 projected rows follow the K rows
+            w.conv_c = w.pw;
+            w.k_floats = (int64_t)w.kd * d.n_ctx + (int64_t)(l.conv_taps - 1) * w.pw;
+        }
+        if (recur || l.conv_taps > 1) a->has_state = true;
+        a->max_cv = std::max(a->max_cv, w.conv_c);
+        if (l.shared_ff > 0) { a->max_ff = std::max(a->max_ff, l.shared_ff); a->max_k = std::max(a->max_k, l.shared_ff); }
         if (latent) {
             a->max_rq = std::max(a->max_rq, l.q_rank);
             a->max_lq = std::max(a->max_lq, l.n_heads * (l.qk_dim + l.rot_dim));
@@ -338,7 +392,11 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
     AL(a->tile_row0, 4 * ntile);
     AL(a->tile_end, 4 * ntile);
     AL(a->n_tiles, 16);
-    AL(a->z, 4 * (size_t)std::max(a->max_e, 1));
+    AL(a->z, 4 * ((size_t)std::max(a->max_e, 1) + 1));
+    if (a->max_cv) AL(a->cv, 4 * (size_t)a->max_cv * B);
+    AL(a->sh, 4 * dim * B);
+    AL(a->ffo, 4 * dim * B);
+    AL(a->sgate, 4 * B);
     a->ldP = (d.n_ctx + PA_DS_KEYS - 1) / PA_DS_KEYS;
     AL(a->pm, 4 * (size_t)a->max_h * a->ldP);
     AL(a->pl, 4 * (size_t)a->max_h * a->ldP);
@@ -362,6 +420,10 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
         cudaFuncSetAttribute(pa_k_dec_expert_up<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_dec_dense_up<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_dec_dense_up<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_tc_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_tc_gemm<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM) != cudaSuccess) {
         cudaGetLastError();
@@ -385,8 +447,15 @@ void ps_arch_destroy(PsArch *a) {
     delete a;
 }
 
-size_t ps_arch_k_bytes(const PsArch *a, int layer) { return 4 * (size_t)a->L[(size_t)layer].kd * (size_t)a->d.n_ctx; }
-size_t ps_arch_v_bytes(const PsArch *a, int layer) { return 4 * (size_t)a->L[(size_t)layer].vd * (size_t)a->d.n_ctx; }
+size_t ps_arch_k_bytes(const PsArch *a, int layer) {
+    const PsArchLayer &w = a->L[(size_t)layer];
+    return 4 * (w.k_floats ? (size_t)w.k_floats : (size_t)w.kd * (size_t)a->d.n_ctx);
+}
+size_t ps_arch_v_bytes(const PsArch *a, int layer) {
+    const PsArchLayer &w = a->L[(size_t)layer];
+    return 4 * (w.v_floats ? (size_t)w.v_floats : (size_t)w.vd * (size_t)a->d.n_ctx);
+}
+bool ps_arch_has_state(const PsArch *a) { return a->has_state; }
 float *ps_arch_logits(PsArch *a) { return a->logits; }
 void ps_arch_set_taps(PsArch *a, int on) { a->taps_on = on; }
 const float *ps_arch_tap(PsArch *a, int layer) { return (a->taps_on && layer >= 0 && (size_t)layer < a->taps.size()) ? a->taps[(size_t)layer] : nullptr; }
@@ -417,7 +486,15 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
     };
     if ((rc = aalloc(a, (void **)&a->embed, 2 * dim * d.vocab_size, err)) || (rc = upload_mat(a->embed, wt->embed, dim * d.vocab_size, "embed", err))) return rc;
     if ((rc = aalloc(a, (void **)&a->head, 2 * dim * d.vocab_size, err)) || (rc = upload_mat(a->head, wt->head, dim * d.vocab_size, "head", err))) return rc;
-    if ((rc = vec(&a->final_norm, wt->final_norm, dim, "final norm", d.norm_unit_offset != 0))) return rc;
+    // a norm's weight: [dim] values, or with norm_scalar one number for all coordinates
+    auto normvec = [&](float **dst, const ps_cuda_tensor &t, const char *what) -> int {
+        int r = small_to_f32(t, d.norm_scalar ? 1 : dim, tmp, what, err);
+        if (r) return r;
+        if (d.norm_scalar) tmp.assign(dim, tmp[0]);
+        if (d.norm_unit_offset) for (float &v : tmp) v = 1.0f + v;
+        return upload_f32(a, dst, tmp, err);
+    };
+    if ((rc = normvec(&a->final_norm, wt->final_norm, "final norm"))) return rc;
     auto mat = [&](bf16 **dst, const ps_cuda_tensor &t, size_t n, const char *what) -> int {
         int r = aalloc(a, (void **)dst, 2 * n, err);
         return r ? r : upload_mat(*dst, t, n, what, err);
@@ -429,7 +506,7 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
         const ps_cuda_arch_layer_weights &s = wt->layers[i];
         char nm[64];
         snprintf(nm, sizeof nm, "layer %d", i);
-        if ((rc = vec(&w.norm, s.norm, dim, nm, d.norm_unit_offset != 0))) return rc;
+        if (!l.raw_input && (rc = normvec(&w.norm, s.norm, nm))) return rc;
         const size_t nq = (size_t)w.qd, nk = (size_t)w.kd, nv = (size_t)w.vd;
         if ((rc = aalloc(a, (void **)&w.wqkv, 2 * (size_t)w.pw * dim, err))) return rc;
         if (l.mixer_kind == PS_MIXER_LATENT) {
@@ -452,15 +529,42 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
                 if ((rc = aalloc(a, (void **)&w.rope_freq, fd.size() * 8, err))) return rc;
                 PA_CK(cudaMemcpy(w.rope_freq, fd.data(), fd.size() * 8, cudaMemcpyHostToDevice));
             }
-        } else if ((rc = upload_mat(w.wqkv, s.q, nq * dim, "q", err)) || (rc = upload_mat(w.wqkv + nq * dim, s.k, nk * dim, "k", err)) ||
-                   (rc = upload_mat(w.wqkv + (nq + nk) * dim, s.v, nv * dim, "v", err)))
-            return rc;
+        } else if (l.mixer_kind == PS_MIXER_MAMBA2) {
+            const size_t H = (size_t)l.n_heads;
+            if ((rc = upload_mat(w.wqkv, s.w_in, (size_t)w.pw * dim, "in", err))) return rc;
+            if ((rc = vec(&w.conv_w, s.conv_w, (size_t)w.conv_c * l.conv_taps, "convolution", false)) || (rc = vec(&w.conv_b, s.conv_b, (size_t)w.conv_c, "convolution bias", false)) ||
+                (rc = vec(&w.dt_bias, s.dt_bias, H, "dt_bias", false)) || (rc = vec(&w.a_log, s.a_log, H, "A_log", false)) || (rc = vec(&w.d_skip, s.d_skip, H, "D", false)) ||
+                (rc = vec(&w.mix_norm, s.mix_norm, (size_t)w.od, "mixer norm", false)))
+                return rc;
+        } else {
+            if ((rc = upload_mat(w.wqkv, s.q, nq * dim, "q", err)) || (rc = upload_mat(w.wqkv + nq * dim, s.k, nk * dim, "k", err)) ||
+                (rc = upload_mat(w.wqkv + (nq + nk) * dim, s.v, nv * dim, "v", err)))
+                return rc;
+            if (l.mixer_kind == PS_MIXER_RETENTION) {
+                if ((rc = upload_mat(w.wqkv + (nq + nk + nv) * dim, s.g, nv * dim, "g", err)) || (rc = vec(&w.decay, s.decay, (size_t)l.n_heads, "decay", false))) return rc;
+                if (l.rope_dims > 0) {
+                    std::vector<double> fd((size_t)l.rope_dims / 2);
+                    rope_freq_host(l.rope_dims, l.rope_base, 0.f, 0, 0.f, 0.f, fd.data());
+                    if ((rc = aalloc(a, (void **)&w.rope_freq, fd.size() * 8, err))) return rc;
+                    PA_CK(cudaMemcpy(w.rope_freq, fd.data(), fd.size() * 8, cudaMemcpyHostToDevice));
+                }
+            }
+            if (w.gen2 && l.qk_norm == PS_QKNORM_WHOLE && ((rc = vec(&w.q_norm, s.q_norm, nq, "q norm", false)) || (rc = vec(&w.k_norm, s.k_norm, nk, "k norm", false)))) return rc;
+            if (w.gen2 && l.mixer_kind == PS_MIXER_ATTENTION && l.conv_taps > 1) {
+                std::vector<float> cw, part;
+                for (auto pr : {std::make_pair(&s.q_conv, nq), std::make_pair(&s.k_conv, nk), std::make_pair(&s.v_conv, nv)}) {
+                    if ((rc = small_to_f32(*pr.first, pr.second * l.conv_taps, part, "convolution", err))) return rc;
+                    cw.insert(cw.end(), part.begin(), part.end());
+                }
+                if ((rc = upload_f32(a, &w.conv_w, cw, err))) return rc;
+            }
+        }
         if ((rc = aalloc(a, (void **)&w.wo, 2 * dim * (size_t)w.od, err)) || (rc = upload_mat(w.wo, s.o, dim * (size_t)w.od, "o", err))) return rc;
         if (l.block_kind == PS_BLOCK_SEQUENTIAL) {
-            if (l.post_norm && (rc = vec(&w.norm_mix_out, s.norm_mix_out, dim, "norm of the mixer's output", d.norm_unit_offset != 0))) return rc;
+            if (l.post_norm && (rc = normvec(&w.norm_mix_out, s.norm_mix_out, "norm of the mixer's output"))) return rc;
             if (l.mlp_kind != PS_MLP_NONE) {
-                if ((rc = vec(&w.norm_ff, s.norm_ff, dim, "norm before the feed-forward", d.norm_unit_offset != 0))) return rc;
-                if (l.post_norm && (rc = vec(&w.norm_ff_out, s.norm_ff_out, dim, "norm of the feed-forward's output", d.norm_unit_offset != 0))) return rc;
+                if (!l.raw_input && (rc = normvec(&w.norm_ff, s.norm_ff, "norm before the feed-forward"))) return rc;
+                if (l.post_norm && (rc = normvec(&w.norm_ff_out, s.norm_ff_out, "norm of the feed-forward's output"))) return rc;
             }
         }
         if (l.log_bias && ((rc = vec(&w.r1, s.r1, (size_t)l.n_heads, "distance-bias slopes", false)) || (rc = vec(&w.r2, s.r2, (size_t)l.n_heads, "distance-bias rates", false)))) return rc;
@@ -487,7 +591,13 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
         if (l.mlp_kind == PS_MLP_ROUTED) {
             const size_t E = (size_t)l.n_experts, ff = (size_t)l.expert_ff;
             if (!s.gate || !s.up || !s.down) return afail(err, PS_CUDA_ERR_INVALID, "bind: layer %d has no expert tensors", i);
-            if ((rc = aalloc(a, (void **)&w.router, 2 * E * dim, err)) || (rc = upload_mat(w.router, s.router, E * dim, "router", err))) return rc;
+            const size_t sgr = (l.shared_ff > 0 && l.shared_gate) ? 1 : 0; // the shared expert's gate is one more router row
+            if ((rc = aalloc(a, (void **)&w.router, 2 * (E + sgr) * dim, err)) || (rc = upload_mat(w.router, s.router, E * dim, "router", err))) return rc;
+            if (sgr && (rc = upload_mat(w.router + E * dim, s.shared_sg, dim, "shared gate", err))) return rc;
+            if (l.shared_ff > 0) {
+                const size_t sf = (size_t)l.shared_ff;
+                if ((rc = mat(&w.wsg, s.shared_gate, sf * dim, "shared gate rows")) || (rc = mat(&w.wsu, s.shared_up, sf * dim, "shared up rows")) || (rc = mat(&w.wsd, s.shared_down, sf * dim, "shared down rows"))) return rc;
+            }
             if ((rc = aalloc(a, (void **)&w.wgate, 2 * E * ff * dim, err)) || (rc = aalloc(a, (void **)&w.wup, 2 * E * ff * dim, err)) ||
                 (rc = aalloc(a, (void **)&w.wdown, 2 * E * ff * dim, err)))
                 return rc;
@@ -520,6 +630,8 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
             if (w.wuq && (rc = tile(&w.t_uq, w.wuq, 1, w.d.n_heads * (w.d.qk_dim + w.d.rot_dim), w.d.q_rank))) return rc;
             if (w.d.mlp_kind == PS_MLP_DENSE &&
                 ((rc = tile(&w.t_gate, w.wgate, 1, w.d.expert_ff, d.dim)) || (rc = tile(&w.t_up, w.wup, 1, w.d.expert_ff, d.dim)) || (rc = tile(&w.t_down, w.wdown, 1, d.dim, w.d.expert_ff))))
+                return rc;
+            if (w.wsg && ((rc = tile(&w.t_sg, w.wsg, 1, w.d.shared_ff, d.dim)) || (rc = tile(&w.t_su, w.wsu, 1, w.d.shared_ff, d.dim)) || (rc = tile(&w.t_sd, w.wsd, 1, d.dim, w.d.shared_ff))))
                 return rc;
             if (w.d.mlp_kind == PS_MLP_ROUTED &&
                 ((rc = tile(&w.t_gate, w.wgate, w.d.n_experts, w.d.expert_ff, d.dim)) || (rc = tile(&w.t_up, w.wup, w.d.n_experts, w.d.expert_ff, d.dim)) ||
@@ -586,7 +698,9 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     };
     // scores -> soft-max -> P.V of a batch against the cache rows 0 .. n_kv - 1 (keys before the first query's window are skipped)
     auto attend = [&](const PaAttn &at, const float *q, int ldq, int kd, int li, int aw) -> int {
-        const int tile0 = (at.window > 0 ? std::max(0, pos0 - at.window + 1) : 0) / PA_TN;
+        int lo0 = at.window > 0 ? std::max(0, pos0 - at.window + 1) : 0; // the first key the first query sees
+        if (at.chunk > 0) lo0 = std::max(lo0, pos0 - pos0 % at.chunk);
+        const int tile0 = lo0 / PA_TN;
         pa_k_scores<<<dim3(cdiv(n_kv, PA_TN) - tile0, cdiv(bs, PA_TM), at.H), blk, 0, st>>>(at, q, ldq, io.kc[li], kd, a->S, io.pos_dev, bs, tile0);
         PA_LAUNCH();
         pa_k_mix_softmax<<<bs, 256, 4 * (size_t)at.H * at.H, st>>>(at, a->S, io.pos_dev, bs);
@@ -598,6 +712,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     // sequential blocks: a sublayer's output waits here until the next seam adds it (normed) to the residual stream
     const float *pend_y = nullptr, *pend_w = nullptr;
     auto seam = [&](float *h_out, const float *w_in) -> int {
+        if (!pend_y && !h_out) return 0;
         pa_k_seam_norm<<<bs, 256, 0, st>>>(a->x, pend_y, pend_w, h_out, w_in, dim, groups, d.norm_eps);
         PA_LAUNCH();
         pend_y = pend_w = nullptr;
@@ -612,8 +727,8 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         pend_y = pend_w = nullptr;
     };
     auto dec_mv = [&](PaMv &mv, size_t smem) -> int {
-        mv.ksplit = pick_ksplit(mv.N, mv.K); mv.prefetch = a->opt_prefetch;
-        pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(mv.N, mv.ksplit, mv.K)), dim3(PA_DV_THREADS), smem, st, mv);
+        mv.ksplit = pick_ksplit(mv.N + mv.E, mv.K); mv.prefetch = a->opt_prefetch;
+        pa_launch_dep(pdl, pa_k_dec_mv<ROUND>, dim3(mv_grid(mv.N + mv.E, mv.ksplit, mv.K)), dim3(PA_DV_THREADS), smem, st, mv);
         PA_LAUNCH();
         return 0;
     };
@@ -621,11 +736,50 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     auto attend_single = [&](const PaAttn &at, const float *q, int li) -> int {
         unsigned blocks = cdiv(n_kv_cap, PA_DS_KEYS);
         if (at.window > 0) blocks = std::min(blocks, cdiv(at.window, PA_DS_KEYS) + 1);
+        if (at.chunk > 0) blocks = std::min(blocks, cdiv(at.chunk, PA_DS_KEYS) + 1);
         pa_launch_dep(pdl, pa_k_dec_scores, dim3(blocks), dim3(256), pa_dec_scores_smem(at.H, at.G, at.dq), st, at, q, (const float *)io.kc[li], io.pos_dev, a->S, io.err_dev);
         PA_LAUNCH();
         pa_launch_dep(pdl, pa_k_dec_pv, dim3(cdiv(at.dv, PA_DP_DIMS), at.G, pa_dec_pv_split(at.H, at.G)), dim3(256), pa_dec_pv_smem(at.H, at.G), st, at, (const float *)a->S, (const float *)io.vct[li], io.pos_dev, a->att,
                       pa_dec_pv_chunk(at.H, at.G), io.err_dev);
         PA_LAUNCH();
+        return 0;
+    };
+    // routed experts of a batch on the input rows X: rows grouped per expert on the device, gate | up with the activation, down into per-slot rows
+    auto routed_batch = [&](const float *X, const PsArchLayer &w) -> int {
+        const ps_cuda_layer_desc &l = w.d;
+        const int top = l.top_k, E = l.n_experts, ff = l.expert_ff, n = bs * top;
+        if (tc) {
+            const int max_tiles = n / PT_N + E + 1, nkb1 = (dim + PT_KB - 1) / PT_KB, nkb2 = (ff + PT_KB - 1) / PT_KB;
+            pa_k_dispatch<<<1, 256, 0, st>>>(a->sel_e, a->sel_w, n, top, E, PT_N, a->row_token, a->row_slot, a->row_w, a->tile_e, a->tile_row0, a->tile_end, a->n_tiles);
+            PA_LAUNCH();
+            pa_k_tc_prep_x<<<dim3((unsigned)nkb1, (unsigned)max_tiles), 256, 0, st>>>(a->tcx, X, dim, n, dim, nkb1, a->n_tiles, a->tile_row0, a->tile_end, a->row_token,
+                                                                                    l.route_on_input ? a->row_w : nullptr);
+            PA_LAUNCH();
+            PtArgs g{};
+            g.a0 = w.t_gate; g.a1 = w.t_up; g.b = a->tcx; g.nkb = nkb1; g.n_rt = (ff + PT_M - 1) / PT_M; g.n_ct = max_tiles; g.n_ct_dev = a->n_tiles;
+            g.tile_e = a->tile_e; g.tile_row0 = a->tile_row0; g.tile_end = a->tile_end; g.M = n; g.N = ff; g.mode = PT_MODE_EXPERT_UP; g.C = a->y; g.ldc = ff;
+            g.act = pa_act_of(l); g.err = io.err_dev;
+            pa_k_tc_gemm<2><<<std::min(a->n_sm, max_tiles * g.n_rt), PT_THREADS, PT_SMEM, st>>>(g);
+            PA_LAUNCH();
+            pa_k_tc_prep_x<<<dim3((unsigned)nkb2, (unsigned)max_tiles), 256, 0, st>>>(a->tcx, a->y, ff, n, ff, nkb2, a->n_tiles, a->tile_row0, a->tile_end, nullptr, nullptr);
+            PA_LAUNCH();
+            PtArgs g2{};
+            g2.a0 = w.t_down; g2.b = a->tcx; g2.nkb = nkb2; g2.n_rt = (dim + PT_M - 1) / PT_M; g2.n_ct = max_tiles; g2.n_ct_dev = a->n_tiles;
+            g2.tile_e = a->tile_e; g2.tile_row0 = a->tile_row0; g2.tile_end = a->tile_end; g2.M = n; g2.N = dim; g2.mode = PT_MODE_EXPERT_DOWN; g2.C = a->slot; g2.ldc = dim;
+            g2.row_token = a->row_token; g2.row_slot = a->row_slot; g2.row_w = a->row_w; g2.top = top; g2.on_input = l.route_on_input; g2.err = io.err_dev;
+            pa_k_tc_gemm<1><<<std::min(a->n_sm, max_tiles * g2.n_rt), PT_THREADS, PT_SMEM, st>>>(g2);
+            PA_LAUNCH();
+        } else {
+            const int max_tiles = n / PA_TM + E + 1;
+            pa_k_dispatch<<<1, 256, 0, st>>>(a->sel_e, a->sel_w, n, top, E, PA_TM, a->row_token, a->row_slot, a->row_w, a->tile_e, a->tile_row0, a->tile_end, a->n_tiles);
+            PA_LAUNCH();
+            pa_k_expert_up<ROUND><<<dim3(cdiv(ff, PA_TN), max_tiles), blk, 0, st>>>(X, dim, a->row_token, a->row_w, a->tile_e, a->tile_row0, a->tile_end, a->n_tiles,
+                                                                                    w.wgate, w.wup, a->y, ff, dim, l.route_on_input, pa_act_of(l));
+            PA_LAUNCH();
+            pa_k_expert_down<ROUND><<<dim3(cdiv(dim, PA_TN), max_tiles), blk, 0, st>>>(a->y, ff, a->row_token, a->row_slot, a->row_w, a->tile_e, a->tile_row0, a->tile_end,
+                                                                                      a->n_tiles, w.wdown, a->slot, top, dim, ff, l.route_on_input);
+            PA_LAUNCH();
+        }
         return 0;
     };
     auto seq_layer = [&](int li) -> int {
@@ -705,7 +859,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             const int ff = l.expert_ff;
             float *xout = xo;
             pa_launch_dep(pdl, pa_k_dec_dense_up<ROUND>, dim3(std::min(cdiv(ff, PA_DV_ROWS / 2), (unsigned)(4 * a->n_sm))), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, (const float *)xc,
-                          pend_y, pend_w, (const float *)w.norm_ff, xout, groups, d.norm_eps, (const bf16 *)w.wgate, (const bf16 *)w.wup, a->y, ff, dim, l.act_limit, l.act_alpha, l.up_shift);
+                          pend_y, pend_w, (const float *)w.norm_ff, xout, groups, d.norm_eps, (const bf16 *)w.wgate, (const bf16 *)w.wup, a->y, ff, dim, pa_act_of(l));
             PA_LAUNCH();
             std::swap(xc, xo);
             PaMv mv{};
@@ -721,15 +875,178 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
                 PA_LAUNCH();
                 PtArgs g{};
                 g.a0 = w.t_gate; g.a1 = w.t_up; g.b = a->tcx; g.nkb = nkb; g.n_rt = (ff + PT_M - 1) / PT_M; g.n_ct = n_ct; g.M = bs; g.N = ff; g.mode = PT_MODE_EXPERT_UP;
-                g.C = a->y; g.ldc = ff; g.limit = l.act_limit; g.alpha = l.act_alpha; g.shift = l.up_shift; g.err = io.err_dev;
+                g.C = a->y; g.ldc = ff; g.act = pa_act_of(l); g.err = io.err_dev;
                 pa_k_tc_gemm<2><<<std::min(a->n_sm, n_ct * g.n_rt), PT_THREADS, PT_SMEM, st>>>(g);
             } else {
-                pa_k_dense_up<ROUND><<<dim3(cdiv(ff, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(a->h, dim, w.wgate, w.wup, a->y, bs, ff, dim, l.act_limit, l.act_alpha, l.up_shift);
+                pa_k_dense_up<ROUND><<<dim3(cdiv(ff, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(a->h, dim, w.wgate, w.wup, a->y, bs, ff, dim, pa_act_of(l));
             }
             PA_LAUNCH();
             if ((rc = linear(a->y, ff, ff, w.wdown, w.t_down, dim, a->slot, dim))) return rc;
             pend_y = a->slot; pend_w = l.post_norm ? w.norm_ff_out : nullptr;
         }
+        return 0;
+    };
+
+    // the gated feed-forward of a batch: gate | up with the activation in the product's epilogue, then down
+    auto dense_batch = [&](const float *X, const bf16 *wg, const bf16 *wu, const bf16 *wd, const uint8_t *tg, const uint8_t *tu, const uint8_t *td, int ff, const PaAct &act,
+                           float *out) -> int {
+        if (tc) {
+            const int nkb = (dim + PT_KB - 1) / PT_KB, n_ct = (bs + PT_N - 1) / PT_N;
+            pa_k_tc_prep_x<<<dim3((unsigned)nkb, (unsigned)n_ct), 256, 0, st>>>(a->tcx, X, dim, bs, dim, nkb, nullptr, nullptr, nullptr, nullptr, nullptr);
+            PA_LAUNCH();
+            PtArgs g{};
+            g.a0 = tg; g.a1 = tu; g.b = a->tcx; g.nkb = nkb; g.n_rt = (ff + PT_M - 1) / PT_M; g.n_ct = n_ct; g.M = bs; g.N = ff; g.mode = PT_MODE_EXPERT_UP;
+            g.C = a->y; g.ldc = ff; g.act = act; g.err = io.err_dev;
+            pa_k_tc_gemm<2><<<std::min(a->n_sm, n_ct * g.n_rt), PT_THREADS, PT_SMEM, st>>>(g);
+        } else {
+            pa_k_dense_up<ROUND><<<dim3(cdiv(ff, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(X, dim, wg, wu, a->y, bs, ff, dim, act);
+        }
+        PA_LAUNCH();
+        return linear(a->y, ff, ff, wd, td, dim, out, dim);
+    };
+    auto scan = [&](const PaScan &sc) -> int {
+        const dim3 grid(cdiv(sc.dv, PA_SC_COLS), (unsigned)sc.H);
+        const size_t smem = pa_scan_smem(sc.dk);
+        if (sc.dk <= 32) pa_k_scan<1><<<grid, 256, smem, st>>>(sc);
+        else if (sc.dk <= 64) pa_k_scan<2><<<grid, 256, smem, st>>>(sc);
+        else if (sc.dk <= 128) pa_k_scan<4><<<grid, 256, smem, st>>>(sc);
+        else pa_k_scan<8><<<grid, 256, smem, st>>>(sc);
+        PA_LAUNCH();
+        return 0;
+    };
+    // A sequential block from the general parts: the sublayers read the residual stream itself (raw_input) or its norm; the mixer is an
+    // attention (optional short convolutions, whole-projection norms, distance-bias table, window / chunks), a retention or a
+    // state-space recurrence; the feed-forward is dense or routed (with an optional shared expert).  Every sublayer's output waits
+    // for the next seam.  Single tokens take the weight-streaming mat-vecs with the seam in their prologues; the small kernels
+    // between them are the batch's own (they read the position from device memory).
+    auto gen_layer = [&](int li) -> int {
+        const PsArchLayer &w = a->L[(size_t)li];
+        const ps_cuda_layer_desc &l = w.d;
+        const int H = l.n_heads;
+        const bool raw = l.raw_input != 0;
+        int rc;
+        if (single) {
+            PaMv mv{};
+            seam_mv(mv, raw ? nullptr : w.norm);
+            mv.W = w.wqkv; mv.N = w.pw; mv.K = dim; mv.y = a->qkv;
+            if ((rc = dec_mv(mv, 4 * (size_t)dim))) return rc;
+        } else {
+            if ((rc = seam(raw ? nullptr : a->h, raw ? nullptr : w.norm))) return rc;
+            if ((rc = linear(raw ? a->x : a->h, dim, dim, w.wqkv, w.t_qkv, w.pw, a->qkv, w.pw))) return rc;
+        }
+        if (l.mixer_kind == PS_MIXER_ATTENTION) {
+            float *q = a->qkv;
+            if (l.conv_taps > 1) {
+                float *tail = io.kc[li] + (int64_t)w.kd * d.n_ctx;
+                pa_k_short_conv<<<dim3(cdiv(w.pw, 256), bs), 256, 0, st>>>(a->qkv, w.pw, w.conv_w, nullptr, w.pw, l.conv_taps, tail, 0, a->cv, w.pw, io.pos_dev);
+                PA_LAUNCH();
+                pa_k_conv_tail<<<cdiv(w.pw, 256), 256, 0, st>>>(a->qkv, w.pw, w.pw, l.conv_taps, tail, io.pos_dev, bs);
+                PA_LAUNCH();
+                q = a->cv;
+            }
+            if (l.qk_norm == PS_QKNORM_WHOLE)
+                pa_k_qkv_whole_norm<<<bs, 256, 0, st>>>(q, w.pw, w.qd, w.kd, w.vd, w.q_norm, w.k_norm, d.norm_eps, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
+            else
+                pa_k_kv_store<<<dim3(cdiv(w.kd + w.vd, 256), bs), 256, 0, st>>>(q, w.pw, w.qd, w.kd, w.vd, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
+            PA_LAUNCH();
+            PaAttn at{};
+            at.H = H; at.G = l.n_kv_heads; at.dq = l.qk_dim; at.dv = l.v_dim; at.scale = l.score_scale; at.rel = w.rel; at.bucket = w.bucket; at.n_bucket = d.n_ctx;
+            at.sink = l.sink != PS_SINK_NONE; at.sink_v = w.sink_v; at.r1 = w.r1; at.r2 = w.r2; at.window = l.window; at.chunk = l.chunk;
+            at.n_ctx = d.n_ctx; at.ldS = a->ldS; at.B = B; at.pm = a->pm; at.pl = a->pl; at.ldP = a->ldP;
+            if (single) rc = attend_single(at, q, li);
+            else rc = attend(at, q, w.pw, w.kd, li, w.aw);
+            if (rc) return rc;
+        } else if (l.mixer_kind == PS_MIXER_RETENTION) {
+            const int dq = l.qk_dim, dv = l.v_dim;
+            const PaRope rope{w.rope_freq, l.rope_dims, 1.0f};
+            pa_k_rope_heads<<<bs, 256, 0, st>>>(a->qkv, w.pw, 2 * H, dq, rope, H, 1.0f / sqrtf((float)dq), io.pos_dev); // q | k rotated, k scaled
+            PA_LAUNCH();
+            PaScan sc{};
+            sc.q = a->qkv; sc.k = a->qkv + w.qd; sc.v = a->qkv + 2 * w.qd; sc.ldq = sc.ldk = sc.ldv = w.pw; sc.q_gs = sc.k_gs = dq;
+            sc.H = sc.G = H; sc.dk = dq; sc.dv = dv; sc.decay = w.decay; sc.S = io.kc[li]; sc.o = a->att; sc.ldo = w.od; sc.pos = io.pos_dev; sc.bs = bs;
+            if ((rc = scan(sc))) return rc;
+            pa_k_gate_norm<<<bs, 256, 0, st>>>(a->att, w.od, a->qkv + 2 * w.qd + w.od, w.pw, w.od, H, nullptr, 0, d.norm_eps, a->att, w.od);
+            PA_LAUNCH();
+        } else { // PS_MIXER_MAMBA2
+            const int inner = w.od, gn = l.ssm_groups * l.ssm_state, T = std::max(1, l.conv_taps);
+            float *tail = io.vct[li];
+            pa_k_short_conv<<<dim3(cdiv(w.conv_c, 256), bs), 256, 0, st>>>(a->qkv + inner, w.pw, w.conv_w, w.conv_b, w.conv_c, T, tail, 1, a->cv, w.conv_c, io.pos_dev);
+            PA_LAUNCH();
+            if (T > 1) {
+                pa_k_conv_tail<<<cdiv(w.conv_c, 256), 256, 0, st>>>(a->qkv + inner, w.pw, w.conv_c, T, tail, io.pos_dev, bs);
+                PA_LAUNCH();
+            }
+            PaScan sc{};
+            sc.q = a->cv + inner + gn; sc.k = a->cv + inner; sc.v = a->cv; sc.ldq = sc.ldk = sc.ldv = w.conv_c; sc.q_gs = sc.k_gs = l.ssm_state;
+            sc.H = H; sc.G = l.ssm_groups; sc.dk = l.ssm_state; sc.dv = l.v_dim; sc.dt = a->qkv + 2 * inner + 2 * gn; sc.lddt = w.pw;
+            sc.dt_bias = w.dt_bias; sc.a_log = w.a_log; sc.d_skip = w.d_skip; sc.S = io.kc[li]; sc.o = a->att; sc.ldo = inner; sc.pos = io.pos_dev; sc.bs = bs;
+            if ((rc = scan(sc))) return rc;
+            pa_k_gate_norm<<<bs, 256, 0, st>>>(a->att, inner, a->qkv, w.pw, inner, l.gate_norm_groups, w.mix_norm, 1, d.norm_eps, a->att, inner);
+            PA_LAUNCH();
+        }
+        if (single) {
+            PaMv mv{};
+            mv.x = a->att; mv.W = w.wo; mv.N = dim; mv.K = w.od; mv.y = a->ao;
+            if ((rc = dec_mv(mv, 0))) return rc;
+        } else if ((rc = linear(a->att, w.od, w.od, w.wo, w.t_o, dim, a->ao, dim))) {
+            return rc;
+        }
+        pend_y = a->ao; pend_w = l.post_norm ? w.norm_mix_out : nullptr;
+        if (l.mlp_kind == PS_MLP_NONE) return 0;
+        const float *w_in = raw ? nullptr : w.norm_ff;
+        const PaAct act = pa_act_of(l);
+        const unsigned up_cap = (unsigned)(4 * a->n_sm);
+        if (l.mlp_kind == PS_MLP_DENSE) {
+            const int ff = l.expert_ff;
+            if (single) {
+                pa_launch_dep(pdl, pa_k_dec_dense_up<ROUND>, dim3(std::min(cdiv(ff, PA_DV_ROWS / 2), up_cap)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, (const float *)xc, pend_y, pend_w, w_in,
+                              xo, groups, d.norm_eps, (const bf16 *)w.wgate, (const bf16 *)w.wup, a->y, ff, dim, act);
+                PA_LAUNCH();
+                std::swap(xc, xo);
+                PaMv mv{};
+                mv.x = a->y; mv.W = w.wdown; mv.N = dim; mv.K = ff; mv.y = a->slot;
+                if ((rc = dec_mv(mv, 0))) return rc;
+            } else {
+                if ((rc = seam(raw ? nullptr : a->h, w_in))) return rc;
+                if ((rc = dense_batch(raw ? a->x : a->h, w.wgate, w.wup, w.wdown, w.t_gate, w.t_up, w.t_down, ff, act, a->slot))) return rc;
+            }
+            pend_y = a->slot; pend_w = l.post_norm ? w.norm_ff_out : nullptr;
+            return 0;
+        }
+        // routed experts (+ shared expert)
+        const int E = l.n_experts, ff = l.expert_ff, top = l.top_k, sff = l.shared_ff;
+        const PaRoute rt = pa_route_of(l);
+        if (single) {
+            PaMv mv{}; // the seam, and the router's logits (+ the shared gate's) from the unrounded input
+            seam_mv(mv, w_in);
+            mv.W = nullptr; mv.N = 0; mv.K = dim; mv.Wr = w.router; mv.E = E + (rt.shared_gate ? 1 : 0); mv.z = a->z;
+            if ((rc = dec_mv(mv, 4 * (size_t)dim))) return rc;
+            if (sff > 0) {
+                pa_launch_dep(pdl, pa_k_dec_dense_up<ROUND>, dim3(std::min(cdiv(sff, PA_DV_ROWS / 2), up_cap)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, (const float *)xc, (const float *)nullptr,
+                              (const float *)nullptr, w_in, (float *)nullptr, groups, d.norm_eps, (const bf16 *)w.wsg, (const bf16 *)w.wsu, a->y, sff, dim, act);
+                PA_LAUNCH();
+                PaMv ms{};
+                ms.x = a->y; ms.W = w.wsd; ms.N = dim; ms.K = sff; ms.y = a->sh;
+                if ((rc = dec_mv(ms, 0))) return rc;
+            }
+            pa_k_dec_expert_up<ROUND><<<dim3(std::min(cdiv(ff, PA_DV_ROWS / 2), (unsigned)std::max(1, 4 * a->n_sm / top)), top), PA_DV_THREADS, 4 * (size_t)dim, st>>>(
+                xc, w_in, d.norm_eps, a->z, rt, w.wgate, w.wup, a->y, ff, dim, l.route_on_input, act, a->sel_e, a->sel_w);
+            PA_LAUNCH();
+            const int ksd = pick_ksplit(dim, ff);
+            pa_k_dec_expert_down<ROUND><<<cdiv(dim, PA_DV_ROWS / ksd), PA_DV_THREADS, 0, st>>>(a->y, a->sel_e, a->sel_w, top, w.wdown, nullptr, nullptr, dim, ff, l.route_on_input, ksd, a->ffo,
+                                                                                               sff > 0 ? a->sh : nullptr, rt.shared_gate ? a->z + E : nullptr);
+            PA_LAUNCH();
+        } else {
+            if ((rc = seam(raw ? nullptr : a->h, w_in))) return rc;
+            const float *X = raw ? a->x : a->h;
+            if (sff > 0 && (rc = dense_batch(X, w.wsg, w.wsu, w.wsd, w.t_sg, w.t_su, w.t_sd, sff, act, a->sh))) return rc;
+            pa_k_router<<<bs, 256, 0, st>>>(X, w.router, dim, rt, a->sel_e, a->sel_w, a->sgate);
+            PA_LAUNCH();
+            if ((rc = routed_batch(X, w))) return rc;
+            pa_k_moe_sum<<<dim3(cdiv(dim, 256), bs), 256, 0, st>>>(a->ffo, a->slot, top, sff > 0 ? a->sh : nullptr, rt.shared_gate ? a->sgate : nullptr, dim);
+            PA_LAUNCH();
+        }
+        pend_y = a->ffo; pend_w = l.post_norm ? w.norm_ff_out : nullptr;
         return 0;
     };
 
@@ -739,7 +1056,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         const PsArchLayer &w = a->L[(size_t)li];
         const ps_cuda_layer_desc &l = w.d;
         if (l.block_kind == PS_BLOCK_SEQUENTIAL) {
-            int rc = seq_layer(li);
+            int rc = w.gen2 ? gen_layer(li) : seq_layer(li);
             if (rc) return rc;
             if (a->taps_on) {
                 if ((rc = seam(nullptr, nullptr))) return rc; // the tap shows the layer's whole effect
@@ -770,8 +1087,8 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
                 cudaStream_t se = a->opt_fork ? a->side : st;
                 if (a->opt_fork) { PA_CK(cudaEventRecord(a->ev_fork, st)); PA_CK(cudaStreamWaitEvent(se, a->ev_fork, 0)); }
                 pa_k_dec_expert_up<ROUND><<<dim3(std::min(cdiv(l.expert_ff, PA_DV_ROWS / 2), (unsigned)std::max(1, 4 * a->n_sm / l.top_k)), l.top_k), PA_DV_THREADS, 4 * (size_t)dim, se>>>(
-                    a->x, w.norm, d.norm_eps, a->z, l.n_experts, l.top_k, l.route_renorm, w.wgate, w.wup, a->y, l.expert_ff, dim, l.route_on_input, l.act_limit, l.act_alpha,
-                    l.up_shift, a->sel_e, a->sel_w);
+                    a->x, w.norm, d.norm_eps, a->z, pa_route_of(l), w.wgate, w.wup, a->y, l.expert_ff, dim, l.route_on_input, pa_act_of(l),
+                    a->sel_e, a->sel_w);
                 if (a->opt_fork) PA_CK(cudaEventRecord(a->ev_join, se));
             }
         } else if (tc) {
@@ -819,48 +1136,19 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         int top = 0;
         if (routed) {
             top = l.top_k;
-            const int E = l.n_experts, ff = l.expert_ff, n = bs * top;
+            const int ff = l.expert_ff;
+            int rc = 0;
             if (!single) {
-                pa_k_router<<<bs, 256, 0, st>>>(a->h, w.router, dim, E, top, l.route_renorm, a->sel_e, a->sel_w);
+                pa_k_router<<<bs, 256, 0, st>>>(a->h, w.router, dim, pa_route_of(l), a->sel_e, a->sel_w, a->sgate);
                 PA_LAUNCH();
             }
             if (single) {
-                (void)n; (void)E;
                 if (a->opt_fork) PA_CK(cudaStreamWaitEvent(st, a->ev_join, 0));
                 const int ksd = pick_ksplit(dim, ff);
                 pa_k_dec_expert_down<ROUND><<<cdiv(dim, PA_DV_ROWS / ksd), PA_DV_THREADS, 0, st>>>(a->y, a->sel_e, a->sel_w, top, w.wdown, a->ao, a->x, dim, ff, l.route_on_input, ksd);
                 PA_LAUNCH();
-            } else if (tc) {
-                const int max_tiles = n / PT_N + E + 1, nkb1 = (dim + PT_KB - 1) / PT_KB, nkb2 = (ff + PT_KB - 1) / PT_KB;
-                pa_k_dispatch<<<1, 256, 0, st>>>(a->sel_e, a->sel_w, n, top, E, PT_N, a->row_token, a->row_slot, a->row_w, a->tile_e, a->tile_row0, a->tile_end, a->n_tiles);
-                PA_LAUNCH();
-                pa_k_tc_prep_x<<<dim3((unsigned)nkb1, (unsigned)max_tiles), 256, 0, st>>>(a->tcx, a->h, dim, n, dim, nkb1, a->n_tiles, a->tile_row0, a->tile_end, a->row_token,
-                                                                                        l.route_on_input ? a->row_w : nullptr);
-                PA_LAUNCH();
-                PtArgs g{};
-                g.a0 = w.t_gate; g.a1 = w.t_up; g.b = a->tcx; g.nkb = nkb1; g.n_rt = (ff + PT_M - 1) / PT_M; g.n_ct = max_tiles; g.n_ct_dev = a->n_tiles;
-                g.tile_e = a->tile_e; g.tile_row0 = a->tile_row0; g.tile_end = a->tile_end; g.M = n; g.N = ff; g.mode = PT_MODE_EXPERT_UP; g.C = a->y; g.ldc = ff;
-                g.limit = l.act_limit; g.alpha = l.act_alpha; g.shift = l.up_shift; g.err = io.err_dev;
-                pa_k_tc_gemm<2><<<std::min(a->n_sm, max_tiles * g.n_rt), PT_THREADS, PT_SMEM, st>>>(g);
-                PA_LAUNCH();
-                pa_k_tc_prep_x<<<dim3((unsigned)nkb2, (unsigned)max_tiles), 256, 0, st>>>(a->tcx, a->y, ff, n, ff, nkb2, a->n_tiles, a->tile_row0, a->tile_end, nullptr, nullptr);
-                PA_LAUNCH();
-                PtArgs g2{};
-                g2.a0 = w.t_down; g2.b = a->tcx; g2.nkb = nkb2; g2.n_rt = (dim + PT_M - 1) / PT_M; g2.n_ct = max_tiles; g2.n_ct_dev = a->n_tiles;
-                g2.tile_e = a->tile_e; g2.tile_row0 = a->tile_row0; g2.tile_end = a->tile_end; g2.M = n; g2.N = dim; g2.mode = PT_MODE_EXPERT_DOWN; g2.C = a->slot; g2.ldc = dim;
-                g2.row_token = a->row_token; g2.row_slot = a->row_slot; g2.row_w = a->row_w; g2.top = top; g2.on_input = l.route_on_input; g2.err = io.err_dev;
-                pa_k_tc_gemm<1><<<std::min(a->n_sm, max_tiles * g2.n_rt), PT_THREADS, PT_SMEM, st>>>(g2);
-                PA_LAUNCH();
-            } else {
-                const int max_tiles = n / PA_TM + E + 1;
-                pa_k_dispatch<<<1, 256, 0, st>>>(a->sel_e, a->sel_w, n, top, E, PA_TM, a->row_token, a->row_slot, a->row_w, a->tile_e, a->tile_row0, a->tile_end, a->n_tiles);
-                PA_LAUNCH();
-                pa_k_expert_up<ROUND><<<dim3(cdiv(ff, PA_TN), max_tiles), blk, 0, st>>>(a->h, dim, a->row_token, a->row_w, a->tile_e, a->tile_row0, a->tile_end, a->n_tiles,
-                                                                                        w.wgate, w.wup, a->y, ff, dim, l.route_on_input, l.act_limit, l.act_alpha, l.up_shift);
-                PA_LAUNCH();
-                pa_k_expert_down<ROUND><<<dim3(cdiv(dim, PA_TN), max_tiles), blk, 0, st>>>(a->y, ff, a->row_token, a->row_slot, a->row_w, a->tile_e, a->tile_row0, a->tile_end,
-                                                                                          a->n_tiles, w.wdown, a->slot, top, dim, ff, l.route_on_input);
-                PA_LAUNCH();
+            } else if ((rc = routed_batch(a->h, w))) {
+                return rc;
             }
         }
         if (!single) {

@@ -36,3 +36,5 @@ const float *ps_arch_tap(PsArch *a, int layer); // [max_batch][dim] of the last 
 int ps_arch_set_option(PsArch *a, const char *name, int value); // 1 = known option
 // the single-token step reads the position from device memory only (it may be captured once and replayed)
 bool ps_arch_step_replayable(const PsArch *a);
+// some layer carries state that cannot be cut back to an earlier position (recurrences, convolution tails)
+bool ps_arch_has_state(const PsArch *a);

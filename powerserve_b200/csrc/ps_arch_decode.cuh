@@ -407,40 +407,27 @@ __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__res
 }
 
 // ---------------------------------------------------------------------------------------------------- routed experts
-// the top_k largest router scores (sigmoid of z, ties: the lower expert), optionally renormalised; one thread
-__device__ __forceinline__ void pa_topk_serial(const float *__restrict__ z, int E, int top, int renorm, float *sc, int *se, float *sw) {
-    for (int e = 0; e < E; e++) sc[e] = 1.0f / (1.0f + expf(-z[e]));
-    float sum = 0.f;
-    for (int r = 0; r < top; r++) {
-        int best = 0;
-        float bv = -1.f;
-        for (int e = 0; e < E; e++)
-            if (sc[e] > bv) { bv = sc[e]; best = e; }
-        se[r] = best;
-        sw[r] = bv;
-        sum += bv;
-        sc[best] = -2.f;
-    }
-    if (renorm)
-        for (int r = 0; r < top; r++) sw[r] /= sum;
-}
-
 // grid (row pairs of ff, top_k): y[r][n] = act(gate_e . z, up_e . z), z = round(w_r * h) (score on the input) or round(h)
 template <bool ROUND>
-__global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_expert_up(const float *__restrict__ x, const float *__restrict__ norm_w, float eps, const float *__restrict__ z, int E,
-                                                                    int top, int renorm, const bf16 *__restrict__ Wg, const bf16 *__restrict__ Wu, float *__restrict__ y,
-                                                                    int ff, int dim, int on_input, float limit, float alpha, float shift, int *__restrict__ sel_e,
+__global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_expert_up(const float *__restrict__ x, const float *__restrict__ norm_w, float eps, const float *__restrict__ z, PaRoute rt,
+                                                                    const bf16 *__restrict__ Wg, const bf16 *__restrict__ Wu, float *__restrict__ y,
+                                                                    int ff, int dim, int on_input, PaAct act, int *__restrict__ sel_e,
                                                                     float *__restrict__ sel_w) {
     extern __shared__ __align__(16) float pa_hs[];
     __shared__ float sc[PA_MAX_EXPERTS];
     __shared__ int se[PA_MAX_EXPERTS];
     __shared__ float sw[PA_MAX_EXPERTS];
     if (threadIdx.x == 0) {
-        pa_topk_serial(z, E, top, renorm, sc, se, sw);
+        pa_route_serial(z, rt, sc, se, sw);
         if (blockIdx.x == 0 && blockIdx.y == 0)
-            for (int r = 0; r < top; r++) { sel_e[r] = se[r]; sel_w[r] = sw[r]; }
+            for (int r = 0; r < rt.top; r++) { sel_e[r] = se[r]; sel_w[r] = sw[r]; }
     }
-    pa_norm_to_smem(pa_hs, x, norm_w, dim, eps); // (its barriers also publish se / sw)
+    if (norm_w) {
+        pa_norm_to_smem(pa_hs, x, norm_w, dim, eps); // (its barriers also publish se / sw)
+    } else { // the experts read the residual stream itself
+        for (int c = threadIdx.x; c < dim; c += blockDim.x) pa_hs[c] = x[c];
+        __syncthreads();
+    }
     const int r = blockIdx.y, e = se[r], lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float w = on_input ? sw[r] : 1.0f;
     // a warp owns one ff row at a time: its gate row and its up row are the pair; the CTAs walk the row groups with the grid's stride
@@ -449,7 +436,7 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_expert_up(const float 
         const bf16 *wg = Wg + ((int64_t)e * ff + n) * dim, *wu = Wu + ((int64_t)e * ff + n) * dim;
         float gsum, usum;
         pa_dot2<ROUND>(wg, wu, pa_hs, dim, w, lane, gsum, usum);
-        if (lane == 0) y[(int64_t)r * ff + n] = pa_expert_act(gsum, usum, limit, alpha, shift);
+        if (lane == 0) y[(int64_t)r * ff + n] = pa_expert_act(gsum, usum, act);
     }
 }
 
@@ -459,7 +446,7 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_expert_up(const float 
 template <bool ROUND>
 __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_dense_up(const float *__restrict__ x, const float *__restrict__ seam_y, const float *__restrict__ seam_w,
                                                                    const float *__restrict__ norm_w, float *__restrict__ x_out, int groups, float eps, const bf16 *__restrict__ Wg,
-                                                                   const bf16 *__restrict__ Wu, float *__restrict__ y, int ff, int dim, float limit, float alpha, float shift) {
+                                                                   const bf16 *__restrict__ Wu, float *__restrict__ y, int ff, int dim, PaAct act) {
     extern __shared__ __align__(16) float pa_hs[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, rows = PA_DV_ROWS / 2;
     {
@@ -472,7 +459,7 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_dense_up(const float *
     for (int n = blockIdx.x * rows + warp; n < ff; n += gridDim.x * rows) {
         float gsum, usum;
         pa_dot2<ROUND>(Wg + (int64_t)n * dim, Wu + (int64_t)n * dim, pa_hs, dim, 1.0f, lane, gsum, usum);
-        if (lane == 0) y[n] = pa_expert_act(gsum, usum, limit, alpha, shift);
+        if (lane == 0) y[n] = pa_expert_act(gsum, usum, act);
     }
 }
 
@@ -481,7 +468,8 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_dense_up(const float *
 template <bool ROUND>
 __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_expert_down(const float *__restrict__ y, const int *__restrict__ sel_e, const float *__restrict__ sel_w, int top,
                                                                       const bf16 *__restrict__ Wd, const float *__restrict__ ao, float *__restrict__ x, int dim, int ff,
-                                                                      int on_input, int ksplit) {
+                                                                      int on_input, int ksplit, float *__restrict__ dst = nullptr, const float *__restrict__ extra = nullptr,
+                                                                      const float *__restrict__ extra_logit = nullptr) {
     __shared__ float part_s[8][2];
     ps_grid_dep_launch(); // the next kernel (the next layer's q|k|v rows, or the head) may start fetching its weights
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -512,6 +500,12 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_expert_down(const floa
         for (int q = 0; q < ksplit; q++) { t0 += part_s[q * pairs + pair][0]; t1 += part_s[q * pairs + pair][1]; }
     }
     if (!live) return;
+    if (dst) { // sequential blocks: the feed-forward's output waits for the next seam; a shared expert's output joins it here
+        const float sg = extra ? (extra_logit ? 1.0f / (1.0f + expf(-extra_logit[0])) : 1.0f) : 0.f;
+        if (lane == 0) dst[n0] = t0 + (extra ? sg * extra[n0] : 0.f);
+        if (lane == 1 && n1 != n0) dst[n1] = t1 + (extra ? sg * extra[n1] : 0.f);
+        return;
+    }
     if (lane == 0) x[n0] += ao[n0] + t0;
     if (lane == 1 && n1 != n0) x[n1] += ao[n1] + t1;
 }

@@ -14,6 +14,13 @@
 #define PA_MAX_HEADS 64
 #define PA_MAX_EXPERTS 256
 
+// activation of a gated unit: PS_ACT_SWISH  g' sigmoid(alpha g') (u' + shift) on g' = min(g, limit), u' = clamp(u, +-limit)
+//                             PS_ACT_GELU_TANH  the tanh form of gelu on g, times u
+struct PaAct {
+    float limit, alpha, shift;
+    int kind;
+};
+
 struct PaAttn {
     int H, G, dq, dv;
     float scale;
@@ -26,6 +33,7 @@ struct PaAttn {
     const float *sink_v;    // ... exp(sink_v[h]) (null: exp(0))
     const float *r1, *r2;   // [H] each or null: score -= r1[h] * ln(1 + r2[h] * distance)
     int window;             // > 0: a query sees the keys at distances 0 .. window - 1 only
+    int chunk;              // > 0: a query sees the keys of its own chunk of positions only (chunks counted from position 0)
     int n_ctx;
     int64_t ldS;            // row stride of the score rows
     int B;                  // rows per head in the score buffer (max_batch)
@@ -298,35 +306,82 @@ __global__ void __launch_bounds__(256) pa_k_linear(const float *__restrict__ A, 
 }
 
 // ---------------------------------------------------------------------------------------------------------------- router
-// scores = sigmoid(W_r h) in fp32; the top_k largest (ties: the lower expert) -> sel_e / sel_w [token][top_k]
-__global__ void __launch_bounds__(256) pa_k_router(const float *__restrict__ h, const bf16 *__restrict__ Wr, int dim, int E, int top, int renorm, int *__restrict__ sel_e,
-                                                   float *__restrict__ sel_w) {
-    __shared__ float sc[PA_MAX_EXPERTS];
+// how a router turns its logits into chosen experts and weights
+struct PaRoute {
+    int E, top;
+    int act;           // PS_ROUTER_SIGMOID: every logit through a sigmoid; PS_ROUTER_SOFTMAX: soft-max over all experts
+    int groups, keep;  // groups > 1: equal groups of neighbouring experts, a group is worth its best score, the `keep` best groups stay
+    int renorm;        // the chosen scores are divided by their sum + eps
+    float eps;
+    int shared_gate;   // the router matrix has one more row: the logit of the shared expert's gate
+};
+// one thread: scores from the logits z, group limit, the top largest (ties: the lower expert) -> se / sw; sc is scratch of E entries,
+// sw doubles as scratch of `groups` entries before it receives the weights
+__device__ __forceinline__ void pa_route_serial(const float *__restrict__ z, const PaRoute &r, float *sc, int *se, float *sw) {
+    const int E = r.E;
+    if (r.act == PS_ROUTER_SOFTMAX) {
+        float m = -INFINITY, sum = 0.f;
+        for (int e = 0; e < E; e++) m = fmaxf(m, z[e]);
+        for (int e = 0; e < E; e++) { sc[e] = expf(z[e] - m); sum += sc[e]; }
+        const float inv = 1.0f / sum;
+        for (int e = 0; e < E; e++) sc[e] *= inv;
+    } else {
+        for (int e = 0; e < E; e++) sc[e] = 1.0f / (1.0f + expf(-z[e]));
+    }
+    if (r.groups > 1) {
+        const int per = E / r.groups;
+        for (int g = 0; g < r.groups; g++) {
+            float w = -1.f;
+            for (int e = g * per; e < (g + 1) * per; e++) w = fmaxf(w, sc[e]);
+            sw[g] = w;
+        }
+        for (int n = 0; n < r.keep; n++) { // the kept groups are marked by a worth of 2 (scores never exceed 1)
+            int best = 0;
+            float bv = -1.f;
+            for (int g = 0; g < r.groups; g++)
+                if (sw[g] <= 1.5f && sw[g] > bv) { bv = sw[g]; best = g; }
+            sw[best] = 2.f;
+        }
+        for (int g = 0; g < r.groups; g++)
+            if (sw[g] <= 1.5f)
+                for (int e = g * per; e < (g + 1) * per; e++) sc[e] = -1.f;
+    }
+    float sum = 0.f;
+    for (int n = 0; n < r.top; n++) {
+        int best = 0;
+        float bv = -1.f;
+        for (int e = 0; e < E; e++)
+            if (sc[e] > bv) { bv = sc[e]; best = e; }
+        se[n] = best;
+        sw[n] = bv;
+        sum += bv;
+        sc[best] = -2.f;
+    }
+    if (r.renorm)
+        for (int n = 0; n < r.top; n++) sw[n] /= sum + r.eps;
+}
+
+// router logits W_r h in fp32 (h unrounded), then pa_route_serial -> sel_e / sel_w [token][top]; with a shared gate the matrix's
+// last row gives sgate[token] = sigmoid(w_sg . h)
+__global__ void __launch_bounds__(256) pa_k_router(const float *__restrict__ h, const bf16 *__restrict__ Wr, int dim, PaRoute r, int *__restrict__ sel_e,
+                                                   float *__restrict__ sel_w, float *__restrict__ sgate) {
+    __shared__ float zs[PA_MAX_EXPERTS + 1], sc[PA_MAX_EXPERTS], sw[PA_MAX_EXPERTS];
+    __shared__ int se[PA_MAX_EXPERTS];
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float *hr = h + (int64_t)t * dim;
-    for (int e = warp; e < E; e += 8) {
+    for (int e = warp; e < r.E + (r.shared_gate ? 1 : 0); e += 8) {
         const bf16 *wr = Wr + (int64_t)e * dim;
         float s = 0.f;
         for (int k = lane; k < dim; k += 32) s = fmaf(__bfloat162float(wr[k]), hr[k], s);
 #pragma unroll
         for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (lane == 0) sc[e] = 1.0f / (1.0f + expf(-s));
+        if (lane == 0) zs[e] = s;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        float sum = 0.f;
-        for (int r = 0; r < top; r++) {
-            int best = 0;
-            float bv = -1.f;
-            for (int e = 0; e < E; e++)
-                if (sc[e] > bv) { bv = sc[e]; best = e; }
-            sel_e[t * top + r] = best;
-            sel_w[t * top + r] = bv;
-            sum += bv;
-            sc[best] = -2.f;
-        }
-        if (renorm)
-            for (int r = 0; r < top; r++) sel_w[t * top + r] /= sum;
+        pa_route_serial(zs, r, sc, se, sw);
+        for (int n = 0; n < r.top; n++) { sel_e[t * r.top + n] = se[n]; sel_w[t * r.top + n] = sw[n]; }
+        if (r.shared_gate) sgate[t] = 1.0f / (1.0f + expf(-zs[r.E]));
     }
 }
 
@@ -358,10 +413,12 @@ __global__ void __launch_bounds__(256) pa_k_dispatch(const int *__restrict__ sel
     }
 }
 
-__device__ __forceinline__ float pa_expert_act(float g, float u, float limit, float alpha, float shift) {
-    g = fminf(g, limit);
-    u = fminf(fmaxf(u, -limit), limit);
-    return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + shift);
+__device__ __forceinline__ float pa_expert_act(float g, float u, PaAct act) {
+    if (act.kind == PS_ACT_GELU_TANH) // 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * u
+        return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    g = fminf(g, act.limit);
+    u = fminf(fmaxf(u, -act.limit), act.limit);
+    return g * (1.0f / (1.0f + expf(-act.alpha * g))) * (u + act.shift);
 }
 
 // y[r][n] = act(gate_e . z_r, up_e . z_r), z_r = w_r * h[token_r] (route_on_input) or h[token_r]
@@ -369,7 +426,7 @@ template <bool ROUND>
 __global__ void __launch_bounds__(256) pa_k_expert_up(const float *__restrict__ h, int ldh, const int *__restrict__ row_token, const float *__restrict__ row_w,
                                                       const int *__restrict__ tile_e, const int *__restrict__ tile_row0, const int *__restrict__ tile_end,
                                                       const int *__restrict__ n_tiles, const bf16 *__restrict__ Wg, const bf16 *__restrict__ Wu, float *__restrict__ y, int ff,
-                                                      int dim, int on_input, float limit, float alpha, float shift) {
+                                                      int dim, int on_input, PaAct act) {
     PA_TILE_SMEM(2);
     if ((int)blockIdx.y >= *n_tiles) return;
     const int tid = threadIdx.x, lr = tid >> 2, tx = tid & 15, ty = tid >> 4;
@@ -388,7 +445,7 @@ __global__ void __launch_bounds__(256) pa_k_expert_up(const float *__restrict__ 
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int n = n0 + tx * 4 + j;
-            if (n < ff) y[(int64_t)r * ff + n] = pa_expert_act(acc[0][i][j], acc[1][i][j], limit, alpha, shift);
+            if (n < ff) y[(int64_t)r * ff + n] = pa_expert_act(acc[0][i][j], acc[1][i][j], act);
         }
     }
 }
@@ -424,7 +481,7 @@ __global__ void __launch_bounds__(256) pa_k_expert_down(const float *__restrict_
 // dense gated feed-forward, first half: y[m][n] = act(gate[n] . h_m, up[n] . h_m)
 template <bool ROUND>
 __global__ void __launch_bounds__(256) pa_k_dense_up(const float *__restrict__ h, int ldh, const bf16 *__restrict__ Wg, const bf16 *__restrict__ Wu, float *__restrict__ y, int M, int ff,
-                                                     int dim, float limit, float alpha, float shift) {
+                                                     int dim, PaAct act) {
     PA_TILE_SMEM(2);
     const int tid = threadIdx.x, lr = tid >> 2, tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * PA_TM, n0 = blockIdx.x * PA_TN;
@@ -439,7 +496,7 @@ __global__ void __launch_bounds__(256) pa_k_dense_up(const float *__restrict__ h
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int n = n0 + tx * 4 + j;
-            if (n < ff) y[(int64_t)m * ff + n] = pa_expert_act(acc[0][i][j], acc[1][i][j], limit, alpha, shift);
+            if (n < ff) y[(int64_t)m * ff + n] = pa_expert_act(acc[0][i][j], acc[1][i][j], act);
         }
     }
 }
@@ -453,7 +510,11 @@ __device__ __forceinline__ float pa_score(const PaAttn &at, float dot, int h, in
     return s;
 }
 // first key a query at position p sees
-__device__ __forceinline__ int pa_first_key(const PaAttn &at, int p) { return at.window > 0 ? max(0, p - at.window + 1) : 0; }
+__device__ __forceinline__ int pa_first_key(const PaAttn &at, int p) {
+    int lo = at.window > 0 ? max(0, p - at.window + 1) : 0;
+    if (at.chunk > 0) lo = max(lo, p - p % at.chunk);
+    return lo;
+}
 __device__ __forceinline__ float pa_sink_logit(const PaAttn &at, int h) { return at.sink_v ? at.sink_v[h] : 0.f; }
 
 // S[h][i][j] = score of query i (position pos[i]) and cache row j <= pos[i], before the heads are mixed

@@ -1,0 +1,207 @@
+// ps_arch_recur.cuh - device code of the layer-list executor's recurrent token mixers and short convolutions (ps_arch.cu).
+//
+// Everything here works on a batch of consecutive tokens of ONE sequence and reads the first token's position from device memory,
+// so the same launches serve prompt portions and the replayed single-token step.  A sequence at position 0 starts from zero state
+// whatever the state buffers hold (a cache set that is used again needs no clearing).
+//
+//   pa_k_short_conv      causal convolution over time on every channel, taps newest last, inputs before the batch from the `tail`
+//                        (the last taps - 1 inputs of the sequence), zeros before position 0; optional bias and silu
+//   pa_k_conv_tail       the tail after the batch
+//   pa_k_qkv_whole_norm  q (all heads) and k RMS-normed as one vector each with weights; K row and V^T column into the cache
+//   pa_k_rope_heads      rotate-half rotation of the first dims of every head, in place, with a scale for the heads from `h_scaled` on
+//   pa_k_scan            S_t = a_t S_(t-1) + k_t (c_t v_t)^T, o_t = S_t^T q_t (+ D v_t): retention (a fixed per head, c = 1) and the
+//                        state-space recurrence (a_t = exp(-exp(A_log) dt_t), c_t = dt_t, dt = softplus(raw + bias)); fp32 state,
+//                        a warp per value column, the state's column in registers, tokens strictly in order (the result does not
+//                        depend on how a prompt was cut)
+//   pa_k_gate_norm       RMS norm in equal parts around a silu gate: (y silu(g)) normed times w, or normed y times silu(g)
+//   pa_k_moe_sum         sum of a token's expert slots (fixed order) plus the gated shared expert
+#pragma once
+
+__device__ __forceinline__ float pa_silu(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float pa_softplus(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+// grid (channels / 256, tokens)
+__global__ void __launch_bounds__(256) pa_k_short_conv(const float *__restrict__ u, int ldu, const float *__restrict__ w, const float *__restrict__ b, int C, int T,
+                                                       const float *__restrict__ tail, int act_silu, float *__restrict__ y, int ldy, const int32_t *__restrict__ pos) {
+    const int t = blockIdx.y, c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= C) return;
+    const int p0 = pos[0];
+    float acc = b ? b[c] : 0.f;
+    for (int j = 0; j < T; j++) {
+        const int s = t - (T - 1) + j; // token of the batch this tap meets (negative: before the batch)
+        float v = 0.f;
+        if (s >= 0) v = u[(int64_t)s * ldu + c];
+        else if (p0 + s >= 0) v = tail[(int64_t)(T - 1 + s) * C + c];
+        acc = fmaf(w[(int64_t)c * T + j], v, acc);
+    }
+    y[(int64_t)t * ldy + c] = act_silu ? pa_silu(acc) : acc;
+}
+
+// a thread per channel; the tail is shifted in place oldest first (entry j takes what lay bs entries later)
+__global__ void __launch_bounds__(256) pa_k_conv_tail(const float *__restrict__ u, int ldu, int C, int T, float *__restrict__ tail, const int32_t *__restrict__ pos, int bs) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= C) return;
+    const int p0 = pos[0];
+    for (int j = 0; j < T - 1; j++) {
+        const int s = bs - (T - 1) + j;
+        float v = 0.f;
+        if (s >= 0) v = u[(int64_t)s * ldu + c];
+        else if (p0 + s >= 0) v = tail[(int64_t)(T - 1 + s) * C + c];
+        tail[(int64_t)j * C + c] = v;
+    }
+}
+
+// one CTA per token; row = [q (qd) | k (kd) | v (vd)]
+__global__ void __launch_bounds__(256) pa_k_qkv_whole_norm(float *__restrict__ qkv, int ld, int qd, int kd, int vd, const float *__restrict__ wq, const float *__restrict__ wk,
+                                                           float eps, float *__restrict__ kc, float *__restrict__ vct, int n_ctx, const int32_t *__restrict__ pos) {
+    __shared__ float red[8];
+    const int t = blockIdx.x, p = pos[t];
+    float *row = qkv + (int64_t)t * ld;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < qd; c += 256) s = fmaf(row[c], row[c], s);
+    const float iq = 1.0f / sqrtf(pa_block_sum(s, red) / (float)qd + eps);
+    for (int c = threadIdx.x; c < qd; c += 256) row[c] = row[c] * iq * wq[c];
+    s = 0.f;
+    for (int c = threadIdx.x; c < kd; c += 256) s = fmaf(row[qd + c], row[qd + c], s);
+    const float ik = 1.0f / sqrtf(pa_block_sum(s, red) / (float)kd + eps);
+    for (int c = threadIdx.x; c < kd; c += 256) kc[(int64_t)p * kd + c] = row[qd + c] * ik * wk[c];
+    for (int c = threadIdx.x; c < vd; c += 256) vct[(int64_t)c * n_ctx + p] = row[qd + kd + c];
+}
+
+// one CTA per token; n_heads heads of hd entries from v[t * ld] on; heads h >= h_scaled are multiplied by `scale` after the rotation
+__global__ void __launch_bounds__(256) pa_k_rope_heads(float *__restrict__ v, int ld, int n_heads, int hd, PaRope rope, int h_scaled, float scale, const int32_t *__restrict__ pos) {
+    const int t = blockIdx.x, p = pos[t], half = rope.dims >> 1;
+    float *row = v + (int64_t)t * ld;
+    for (int e = threadIdx.x; e < n_heads * hd; e += 256) {
+        const int hh = e / hd, c = e % hd;
+        const float sc = hh >= h_scaled ? scale : 1.0f;
+        float *x = row + hh * hd;
+        if (c >= rope.dims) { x[c] *= sc; continue; }
+        if (c >= half) continue; // written by its partner
+        const double turns = (double)p * rope.freq[c];
+        const float ang = (float)fma(-rint(turns * 0.15915494309189535), 6.283185307179586, turns);
+        const float cs = cosf(ang) * rope.mscale, sn = sinf(ang) * rope.mscale;
+        const float a = x[c], b = x[c + half];
+        x[c] = (a * cs - b * sn) * sc;
+        x[c + half] = (b * cs + a * sn) * sc;
+    }
+}
+
+#define PA_SC_TOK 32  // tokens staged per round
+#define PA_SC_COLS 8  // value columns per CTA (a warp each)
+struct PaScan {
+    const float *q, *k, *v;   // q[t * ldq + g * q_gs + i], k likewise (i < dk, g = the head's group), v[t * ldv + h * dv + j]
+    int ldq, ldk, ldv, q_gs, k_gs;
+    int H, G, dk, dv;
+    const float *decay;       // [H]: a_t = decay[h], c_t = 1 (dt null)
+    const float *dt;          // dt[t * lddt + h] raw step sizes: c_t = softplus(dt + dt_bias[h]), a_t = exp(-exp(a_log[h]) c_t)
+    int lddt;
+    const float *dt_bias, *a_log, *d_skip; // [H]; d_skip null: no skip term
+    float *S;                 // [H][dk][dv]
+    float *o;                 // o[t * ldo + h * dv + j]
+    int ldo;
+    const int32_t *pos;
+    int bs;
+};
+static inline size_t pa_scan_smem(int dk) { return 4 * ((size_t)2 * PA_SC_TOK * dk + (size_t)PA_SC_TOK * (2 * PA_SC_COLS + 2)); }
+
+// grid (dv / PA_SC_COLS, H); R = state entries per lane = ceil(dk / 32)
+template <int R>
+__global__ void __launch_bounds__(256) pa_k_scan(const PaScan a) {
+    extern __shared__ __align__(16) float sm[];
+    const int dk = a.dk, dv = a.dv;
+    float *qs = sm, *ks = qs + PA_SC_TOK * dk, *vs = ks + PA_SC_TOK * dk, *os = vs + PA_SC_TOK * PA_SC_COLS, *as = os + PA_SC_TOK * PA_SC_COLS, *cs = as + PA_SC_TOK;
+    const int h = blockIdx.y, g = h / (a.H / a.G), j0 = blockIdx.x * PA_SC_COLS, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, j = j0 + warp;
+    const bool fresh = a.pos[0] == 0;
+    float S[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+        const int i = lane + 32 * r;
+        S[r] = (!fresh && i < dk && j < dv) ? a.S[((int64_t)h * dk + i) * dv + j] : 0.f;
+    }
+    const float rate = a.dt ? expf(a.a_log[h]) : 0.f, bias = a.dt ? a.dt_bias[h] : 0.f, fixed = a.dt ? 0.f : a.decay[h], skip = a.d_skip ? a.d_skip[h] : 0.f;
+    for (int t0 = 0; t0 < a.bs; t0 += PA_SC_TOK) {
+        const int nt = min(PA_SC_TOK, a.bs - t0);
+        __syncthreads(); // the round before has been written out
+        for (int e = tid; e < nt * dk; e += 256) {
+            const int tt = e / dk, i = e % dk;
+            qs[e] = a.q[(int64_t)(t0 + tt) * a.ldq + g * a.q_gs + i];
+            ks[e] = a.k[(int64_t)(t0 + tt) * a.ldk + g * a.k_gs + i];
+        }
+        for (int e = tid; e < nt * PA_SC_COLS; e += 256) {
+            const int tt = e / PA_SC_COLS, c = e % PA_SC_COLS;
+            vs[e] = j0 + c < dv ? a.v[(int64_t)(t0 + tt) * a.ldv + h * dv + j0 + c] : 0.f;
+        }
+        for (int tt = tid; tt < nt; tt += 256) {
+            if (a.dt) {
+                const float d = pa_softplus(a.dt[(int64_t)(t0 + tt) * a.lddt + h] + bias);
+                cs[tt] = d;
+                as[tt] = expf(-rate * d);
+            } else {
+                cs[tt] = 1.0f;
+                as[tt] = fixed;
+            }
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; tt++) {
+            const float aa = as[tt], x = vs[tt * PA_SC_COLS + warp], vv = x * cs[tt];
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const int i = lane + 32 * r;
+                if (i < dk) {
+                    S[r] = fmaf(aa, S[r], ks[tt * dk + i] * vv);
+                    acc = fmaf(S[r], qs[tt * dk + i], acc);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) os[tt * PA_SC_COLS + warp] = fmaf(skip, x, acc);
+        }
+        __syncthreads();
+        for (int e = tid; e < nt * PA_SC_COLS; e += 256) {
+            const int tt = e / PA_SC_COLS, c = e % PA_SC_COLS;
+            if (j0 + c < dv) a.o[(int64_t)(t0 + tt) * a.ldo + h * dv + j0 + c] = os[e];
+        }
+    }
+    if (j < dv) {
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const int i = lane + 32 * r;
+            if (i < dk) a.S[((int64_t)h * dk + i) * dv + j] = S[r];
+        }
+    }
+}
+
+// one CTA per token; `width` entries in `parts` equal parts.  gate_first: out = N(y silu(g)) * w; else out = N(y) * silu(g) (w null: 1)
+__global__ void __launch_bounds__(256) pa_k_gate_norm(const float *__restrict__ y, int ldy, const float *__restrict__ gate, int ldg, int width, int parts,
+                                                      const float *__restrict__ w, int gate_first, float eps, float *__restrict__ out, int ldo) {
+    __shared__ float red[8];
+    const int t = blockIdx.x, ps = width / parts;
+    const float *yr = y + (int64_t)t * ldy, *gr = gate + (int64_t)t * ldg;
+    float *orow = out + (int64_t)t * ldo;
+    for (int p = 0; p < parts; p++) {
+        const int c0 = p * ps;
+        float s = 0.f;
+        for (int c = threadIdx.x; c < ps; c += 256) {
+            const float v = gate_first ? yr[c0 + c] * pa_silu(gr[c0 + c]) : yr[c0 + c];
+            s = fmaf(v, v, s);
+        }
+        const float inv = 1.0f / sqrtf(pa_block_sum(s, red) / (float)ps + eps);
+        for (int c = threadIdx.x; c < ps; c += 256) {
+            const float gsl = pa_silu(gr[c0 + c]), wv = w ? w[c0 + c] : 1.0f;
+            orow[c0 + c] = gate_first ? yr[c0 + c] * gsl * inv * wv : yr[c0 + c] * inv * wv * gsl;
+        }
+    }
+}
+
+// out[t][c] = sum_r slot[t][r][c] + sgate[t] * shared[t][c]   (shared null: no shared expert; sgate null: 1)
+__global__ void __launch_bounds__(256) pa_k_moe_sum(float *__restrict__ out, const float *__restrict__ slot, int top, const float *__restrict__ shared,
+                                                    const float *__restrict__ sgate, int dim) {
+    const int t = blockIdx.y, c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= dim) return;
+    float y = 0.f;
+    for (int r = 0; r < top; r++) y += slot[((int64_t)t * top + r) * dim + c];
+    if (shared) y += (sgate ? sgate[t] : 1.0f) * shared[(int64_t)t * dim + c];
+    out[(int64_t)t * dim + c] = y;
+}

@@ -80,7 +80,7 @@ struct PtArgs {
     const int *row_token, *row_slot;
     const float *row_w;
     int top, on_input;
-    float limit, alpha, shift;
+    PaAct act;
     int *err;
 };
 
@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(PT_THREADS, 1) pa_k_tc_gemm(const PtArgs a) {
                         if (a.mode == PT_MODE_DENSE) {
                             a.C[(int64_t)r * a.ldc + n] = acc + bias;
                         } else if (a.mode == PT_MODE_EXPERT_UP) {
-                            a.C[(int64_t)r * a.ldc + n] = pa_expert_act(acc, NA == 2 ? __uint_as_float(w2[c]) : 0.f, a.limit, a.alpha, a.shift);
+                            a.C[(int64_t)r * a.ldc + n] = pa_expert_act(acc, NA == 2 ? __uint_as_float(w2[c]) : 0.f, a.act);
                         } else {
                             a.C[((int64_t)a.row_token[r] * a.top + a.row_slot[r]) * a.ldc + n] = a.on_input ? acc : acc * a.row_w[r];
                         }

@@ -1679,6 +1679,8 @@ int ps_cuda_kv_reset(ps_cuda_ctx *ctx) {
 }
 int ps_cuda_kv_rollback(ps_cuda_ctx *ctx, int n) {
     if (n < 0 || n > ctx->position) return fail(ctx, PS_CUDA_ERR_INVALID, "kv_rollback: %d > position %d (POWERSERVE_ASSERT_KVCACHE)", n, ctx->position);
+    if (ctx->arch && ps_arch_has_state(ctx->arch) && n > 0 && n < ctx->position)
+        return fail(ctx, PS_CUDA_ERR_UNSUPPORTED, "kv_rollback: the model's recurrent state can only be cut back to position 0");
     ctx->position -= n;
     kv_set_mask(ctx, ctx->position, ctx->position + n, 1); // rollback_tokens, kv_cache.hpp:255-263
     return 0;
