@@ -1,9 +1,12 @@
-"""bench.py --arch nufusun | vanapel: prefill and decode throughput of a layer-list design at layer sizes that resemble real
+"""bench.py --arch nufusun | vanapel | dozotar: prefill and decode throughput of a layer-list design at layer sizes that resemble real
 models (random weights), beside the closest existing model of the framework.
 
 --arch vanapel: the Vanapel design (windowed attention layers and one latent-attention layer, dense gated feed-forward) beside
 Nufusun at equal width, head geometry, layer count, vocabulary and as many ACTIVE feed-forward rows per token (top_k x expert
 ff = ff) - the same executor, kernels and bfloat16 weights, so the two steps move nearly the same bytes.
+
+--arch dozotar: the Dozotar design (retention, state-space and chunked-attention layers; dense gelu and routed feed-forwards with a
+shared expert) beside Nufusun at equal width, attention head geometry, layer count, vocabulary and ACTIVE feed-forward rows per token.
 
 --arch nufusun: prefill and decode throughput of the Nufusun design at layer sizes that resemble real models
 (random weights), beside the closest existing model of the framework - a llama stack (Q4_K) with the same width, head
@@ -192,12 +195,84 @@ def run_size_vanapel(name, prompt_len, steps, warmup, seed, chunk):
     out["peaks"] = {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": src}
     return out
 
+# name: (width, attention (heads, kv heads, head size, chunk), retention (heads, dim, vdim), state space (heads, vdim, state, groups), ff, layer types, vocab)
+DOZOTAR_SIZES = {
+    "s": (1024, (16, 4, 64, 512), (8, 64, 128), (32, 64, 128, 2), 1024, "rmma", 32000),
+    "m": (2048, (16, 4, 128, 1024), (8, 128, 256), (64, 64, 128, 4), 2816, "rmma", 32000),
+    "l": (4096, (32, 8, 128, 1024), (16, 128, 256), (128, 64, 128, 8), 7168, "rma", 32000),
+}
+
+
+def run_size_dozotar(name, prompt_len, steps, warmup, seed, chunk):
+    W, (H, G, hs, ck), (RH, rd, rv), (MH, mp, N, mg), ff, kinds, V = DOZOTAR_SIZES[name]
+    hbm, tflops, src = _peaks()
+    n_ctx = -(-(prompt_len + steps + warmup + 24) // 256) * 256
+    prompt = [int(v) for v in np.random.default_rng(1234).integers(0, V, prompt_len)]
+    E, top = 8, 2
+    out = {"size": name, "width": W, "attention": [H, G, hs, ck], "retention": [RH, rd, rv], "state_space": [MH, mp, N, mg], "ff": ff, "experts": [E, top, ff // 2, ff],
+           "layers": kinds, "vocab": V, "context": prompt_len}
+    # the first layer's feed-forward is dense (2 ff rows), the others route 2 of 8 experts of ff / 2 rows beside a shared expert of ff rows: 2 ff active rows everywhere
+    moe = dict(ff=ff // 2, experts=E, top=top, route_groups=4, route_keep=2, shared_ff=ff)
+    layers = []
+    for i, k in enumerate(kinds):
+        mlp = dict(ff=2 * ff) if i == 0 else moe
+        if k == "r":
+            layers.append(arch_synth.dozotar_retention_layer(RH, rd, rv, rot_base=1e6, **mlp))
+        elif k == "m":
+            layers.append(arch_synth.dozotar_mamba2_layer(MH, mp, N, groups=mg, norm_groups=mg, conv=4, **mlp))
+        else:
+            layers.append(arch_synth.dozotar_attention_layer(H, G, hs, hs, chunk=ck, conv=4, bias_max=float(ck), **mlp))
+    cfg = arch_synth.dozotar_config(W, V, layers)
+    m = _load_synth(cfg, arch_synth.dozotar_weights(cfg, seed=seed, rel_rows=32, fast=True), chunk, n_ctx)
+    t_pre, t_dec, launches, e2e = _measure(m, prompt, chunk, steps, warmup)
+    m.close()
+    na, nr, nm, nl = kinds.count("a"), kinds.count("r"), kinds.count("m"), len(kinds)
+    inner = MH * mp
+    p_att = (H + 2 * G) * hs * W + H * hs * W
+    p_ret = (2 * RH * rd + 2 * RH * rv) * W + RH * rv * W
+    p_mam = (2 * inner + 2 * mg * N + MH) * W + inner * W
+    p_ff = 3 * 2 * ff * W + (nl - 1) * ((E + 1) * W + top * 3 * (ff // 2) * W + 3 * ff * W)
+    act_params = na * p_att + nr * p_ret + nm * p_mam + p_ff + V * W
+    keys = min(ck, prompt_len)
+    state_bytes = na * 2 * G * hs * 4 * keys + nr * 2 * RH * rd * rv * 4 + nm * 2 * MH * N * mp * 4        # K / V rows read; recurrent state read and written
+    mix_flops = na * 2 * 2 * H * hs * keys / 2 + nr * 4 * RH * rd * rv + nm * 4 * MH * N * mp                # per token
+    out["dozotar"] = {
+        "prefill_tok_s": prompt_len / t_pre, "prefill_chunk": chunk,
+        "prefill_tflops": (2 * act_params + mix_flops) * prompt_len / t_pre / 1e12,
+        "prefill_frac_of_bf16_peak": (2 * act_params + mix_flops) * prompt_len / t_pre / 1e12 / tflops,
+        "decode_tok_s": 1 / t_dec, "decode_ms": t_dec * 1e3, "decode_launches_per_step": launches,
+        "decode_bytes_per_token": 2 * act_params + state_bytes, "decode_frac_of_hbm_peak": (2 * act_params + state_bytes) / t_dec / 1e9 / hbm,
+        "e2e_decode_tok_s": e2e}
+
+    # ---- the closest existing model: Nufusun, 8 experts of ff rows, the best 2 active
+    ncfg = arch_synth.nufusun_config(W, V, [arch_synth.nufusun_layer(H, G, hs, hs, bias_max=float(prompt_len), experts=E, top=top, ff=ff, limit=7.0) for _ in range(nl)])
+    m = _load_synth(ncfg, arch_synth.nufusun_weights(ncfg, seed=seed, rel_rows=32, fast=True), chunk, n_ctx)
+    t_pre_n, t_dec_n, launches_n, e2e_n = _measure(m, prompt, chunk, steps, warmup)
+    m.close()
+    n_params = nl * (p_att + E * W + top * 3 * ff * W) + V * W
+    n_kv = nl * 2 * G * hs * 4 * prompt_len
+    n_flops = nl * 2 * 2 * H * hs * prompt_len / 2
+    out["nufusun"] = {
+        "prefill_tok_s": prompt_len / t_pre_n, "prefill_chunk": chunk,
+        "prefill_tflops": (2 * n_params + n_flops) * prompt_len / t_pre_n / 1e12,
+        "prefill_frac_of_bf16_peak": (2 * n_params + n_flops) * prompt_len / t_pre_n / 1e12 / tflops,
+        "decode_tok_s": 1 / t_dec_n, "decode_ms": t_dec_n * 1e3, "decode_launches_per_step": launches_n,
+        "decode_bytes_per_token": 2 * n_params + n_kv, "decode_frac_of_hbm_peak": (2 * n_params + n_kv) / t_dec_n / 1e9 / hbm,
+        "e2e_decode_tok_s": e2e_n}
+    out["peaks"] = {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": src}
+    return out
+
 
 def main(args) -> int:
     if capi.load_library().ps_cuda_device_count() == 0:
         print(json.dumps({"arch": args.arch, "unavailable": "no CUDA device: there is no CPU fallback"}))
         return 1
     sizes = [s for s in args.arch_sizes.split(",") if s]
+    if args.arch == "dozotar":
+        res = [run_size_dozotar(s, args.arch_prompt, max(args.steps, 8), max(args.warmup, 3), args.seed, args.arch_chunk) for s in sizes]
+        print(json.dumps({"arch": "dozotar", "dtype": "bf16", "data": "synthetic", "timing": "CUDA events around every call, warm-up first; weights exceed L2",
+                          "sizes": res}))
+        return 0
     if args.arch == "vanapel":
         res = [run_size_vanapel(s, args.arch_prompt, max(args.steps, 8), max(args.warmup, 3), args.seed, args.arch_chunk) for s in sizes]
         print(json.dumps({"arch": "vanapel", "dtype": "bf16", "data": "synthetic", "timing": "CUDA events around every call, warm-up first; weights exceed L2",

@@ -143,3 +143,106 @@ def vanapel_weights(cfg: dict, seed: int = 0, fast: bool = False) -> Dict[str, n
             t[p + "norm2"], t[p + "norm2b"] = norm_w(W), norm_w(W, 0.5)
             t[p + "mlp.gate"], t[p + "mlp.up"], t[p + "mlp.down"] = mat(ff, W, 1.5), mat(ff, W, 1.5), mat(W, ff)
     return t
+
+
+# ------------------------------------------------------------------------------------------------------------ Dozotar
+def _dozotar_mlp(ff: int = 0, experts: int = 0, top: int = 1, route_groups: int = 1, route_keep: int = 1, shared_ff: int = 0) -> Optional[dict]:
+    """ff == 0: no feed-forward; experts == 0: dense of ff rows; else routed experts of ff rows (+ a shared expert of shared_ff rows)"""
+    if not ff:
+        return None
+    if not experts:
+        return {"kind": "dense", "ff": ff}
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "groups": {"count": route_groups, "keep": route_keep}}}
+    if shared_ff:
+        mlp["shared"] = {"ff": shared_ff}
+    return mlp
+
+
+def dozotar_attention_layer(heads: int, kv_heads: int, dim: int, vdim: int, *, chunk: int, conv: int = 3, scale: Optional[float] = None, bias_max: float = 100.0, **mlp) -> dict:
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv, "mask": {"size": chunk}, "bias_max": bias_max,
+             "scale": float(scale if scale is not None else dim ** -0.5)}
+    return {"type": "attention", "mixer": mixer, "mlp": _dozotar_mlp(**mlp)}
+
+
+def dozotar_retention_layer(heads: int, dim: int, vdim: int, *, decay: Optional[List[float]] = None, rot_dims: Optional[int] = None, rot_base: float = 10000.0, **mlp) -> dict:
+    decay = decay if decay is not None else [1.0 - 2.0 ** (-4 - h) for h in range(heads)]
+    mixer = {"heads": heads, "dim": dim, "vdim": vdim, "decay": [float(x) for x in decay], "rot": {"base": rot_base, "dims": dim if rot_dims is None else rot_dims}}
+    return {"type": "retention", "mixer": mixer, "mlp": _dozotar_mlp(**mlp)}
+
+
+def dozotar_mamba2_layer(heads: int, vdim: int, state: int, *, groups: int = 1, norm_groups: int = 1, conv: int = 4, **mlp) -> dict:
+    mixer = {"heads": heads, "vdim": vdim, "state": state, "groups": groups, "norm_groups": norm_groups, "conv": conv}
+    return {"type": "mamba2", "mixer": mixer, "mlp": _dozotar_mlp(**mlp)}
+
+
+def dozotar_config(width: int, vocab: int, layers: List[dict], *, eps: float = 1e-6) -> dict:
+    return {"architecture": "Dozotar", "layers": layers, "norm": {"eps": eps}, "vocab": vocab, "width": width}
+
+
+def dozotar_weights(cfg: dict, seed: int = 0, rel_rows: int = 16, fast: bool = False) -> Dict[str, np.ndarray]:
+    """float32 arrays of bfloat16-representable values keyed by tensor name (fast = True: big matrices as random bfloat16 bit patterns)"""
+    rng = np.random.default_rng(seed)
+    W, V = cfg["width"], cfg["vocab"]
+
+    def rnd(a):
+        return (safetensors.float32_to_bf16_bits(np.asarray(a, np.float32)).astype(np.uint32) << 16).view(np.float32)
+
+    def mat(out_dim, in_dim, gain=1.0):
+        if fast:
+            e = int(np.floor(np.log2(gain / np.sqrt(in_dim)))) + 127
+            bits = rng.integers(0, 1 << 7, size=(out_dim, in_dim), dtype=np.uint16) | np.uint16(e << 7)
+            return bits | (rng.integers(0, 2, size=(out_dim, in_dim), dtype=np.uint16) << 15).astype(np.uint16)
+        return rnd(rng.standard_normal((out_dim, in_dim), dtype=np.float32) * np.float32(gain / np.sqrt(in_dim)))
+
+    def scalar(mean):
+        return rnd(np.array(mean + 0.2 * rng.standard_normal(), np.float32))
+
+    def unit(n):
+        return {"gate": mat(n, W, 1.5), "up": mat(n, W, 1.5), "down": mat(W, n)}
+
+    t: Dict[str, np.ndarray] = {"embed": mat(V, W, np.sqrt(W)), "final.norm": scalar(1.0), "head": mat(V, W)}
+    for i, l in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", l["mixer"]
+        H, dv = m["heads"], m["vdim"]
+        t[p + "norm1"] = scalar(0.8)
+        if l["type"] == "attention":
+            G, dq, taps = m["kv_heads"], m["dim"], m["conv"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"] = mat(H * dq, W), mat(G * dq, W), mat(G * dv, W)
+            t[p + "mix.q.norm"], t[p + "mix.k.norm"] = rnd(1.0 + 0.2 * rng.standard_normal(H * dq)), rnd(1.0 + 0.2 * rng.standard_normal(G * dq))
+            for n, k in (("q", H * dq), ("k", G * dq), ("v", G * dv)) if taps else ():
+                t[p + f"mix.{n}.conv"] = rnd(rng.standard_normal((k, taps)) * 0.5 + np.eye(taps)[taps - 1])
+            t[p + "mix.rel"] = rnd(rng.standard_normal((rel_rows, H)) * 0.7)
+            t[p + "mix.o"] = mat(W, H * dv)
+        elif l["type"] == "retention":
+            dq = m["dim"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.v"], t[p + "mix.g"] = mat(H * dq, W), mat(H * dq, W), mat(H * dv, W), mat(H * dv, W)
+            t[p + "mix.o"] = mat(W, H * dv)
+        else:
+            N, G, taps = m["state"], m["groups"], m["conv"]
+            inner, ch = H * dv, H * dv + 2 * G * N
+            t[p + "mix.in"] = mat(2 * inner + 2 * G * N + H, W)
+            t[p + "mix.conv"] = rnd(rng.standard_normal((ch, taps)) * 0.4 + np.eye(taps)[taps - 1])
+            t[p + "mix.conv.b"] = rnd(rng.standard_normal(ch) * 0.1)
+            t[p + "mix.dt_bias"] = rnd(rng.uniform(-3.0, 0.5, H))
+            t[p + "mix.A_log"] = rnd(np.log(rng.uniform(0.5, 8.0, H)))
+            t[p + "mix.D"] = rnd(1.0 + 0.2 * rng.standard_normal(H))
+            t[p + "mix.norm"] = rnd(1.0 + 0.2 * rng.standard_normal(inner))
+            t[p + "mix.o"] = mat(W, inner)
+        mlp = l.get("mlp")
+        if mlp is None:
+            continue
+        t[p + "norm2"] = scalar(0.8)
+        if mlp["kind"] == "dense":
+            for f, a in unit(mlp["ff"]).items():
+                t[p + "mlp." + f] = a
+        else:
+            E = mlp["router"]["experts"]
+            t[p + "mlp.router"] = mat(E, W, 3.0)
+            for e in range(E):
+                for f, a in unit(mlp["expert"]["ff"]).items():
+                    t[p + f"mlp.e{e}.{f}"] = a
+            if mlp.get("shared"):
+                for f, a in unit(mlp["shared"]["ff"]).items():
+                    t[p + "mlp.shared." + f] = a
+                t[p + "mlp.shared.sg"] = mat(1, W, 2.0)
+    return t
