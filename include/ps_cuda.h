@@ -240,11 +240,11 @@ int ps_cuda_tp_import(ps_cuda_ctx *ctx, const void *handles, int n);
  *                vector each with the weights q_norm / k_norm.
  *   retention  - PS_MIXER_RETENTION: per head S_t = decay[h] S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, no soft-max; q and k
  *                rotated (rotation below, rope_dims of qk_dim), k times qk_dim^(-1/2); every head's o divided by its root mean
- *                square, the concatenation times silu(W_g h), then the output projection.  State: S [H][qk_dim][v_dim] fp32.
+ *                square, the concatenation times silu(W_g h), then the output projection.  State: S per head, qk_dim x v_dim, fp32.
  *   mamba2     - PS_MIXER_MAMBA2: W_in h = [z | x | B | C | dt] (inner = n_heads * v_dim, B and C of ssm_groups * ssm_state);
  *                x|B|C through a causal convolution of conv_taps taps with bias and silu; dt = softplus(dt + dt_bias);
  *                S_t = exp(-exp(A_log[h]) dt) S_(t-1) + dt B_t x_t^T, y_t = S_t^T C_t + D[h] x_t; y silu(z) is RMS-normed in
- *                gate_norm_groups equal parts times mix_norm, then the output projection.  State: S [H][ssm_state][v_dim] fp32
+ *                gate_norm_groups equal parts times mix_norm, then the output projection.  State: S per head, ssm_state x v_dim, fp32,
  *                and the last conv_taps - 1 inputs of the convolution.
  *   recurrent state lives where a cache set keeps an attention layer's K rows (first buffer) and V^T rows (second buffer);
  *                a sequence at position 0 starts from zero state whatever the buffers hold; ps_cuda_kv_rollback to a

@@ -321,16 +321,16 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
         w.qd = l.n_heads * a_dq; w.kd = l.n_kv_heads * a_dq; w.vd = l.n_kv_heads * a_dv; w.od = l.n_heads * l.v_dim;
         w.pw = latent ? l.q_rank + l.kv_rank + l.rot_dim : w.qd + w.kd + w.vd;
         w.aw = l.n_heads * a_dv;
-        if (l.mixer_kind == PS_MIXER_RETENTION) { // q | k | v | gate; the state S [H][qk_dim][v_dim] takes the place of the K rows
+        if (l.mixer_kind == PS_MIXER_RETENTION) { // q | k | v | gate; the state S [H][v_dim][qk_dim padded] takes the place of the K rows
             w.qd = w.kd = l.n_heads * l.qk_dim; w.vd = w.od = w.aw = l.n_heads * l.v_dim;
             w.pw = 2 * w.qd + 2 * w.od;
-            w.k_floats = (int64_t)l.n_heads * l.qk_dim * l.v_dim; w.v_floats = 4;
-        } else if (l.mixer_kind == PS_MIXER_MAMBA2) { // z | x | B | C | dt; S [H][state][v_dim], and the convolution's tail in the second buffer
+            w.k_floats = (int64_t)l.n_heads * pa_scan_dkp(l.qk_dim) * l.v_dim; w.v_floats = 4;
+        } else if (l.mixer_kind == PS_MIXER_MAMBA2) { // z | x | B | C | dt; S [H][v_dim][state padded], and the convolution's tail in the second buffer
             const int inner = l.n_heads * l.v_dim, gn = l.ssm_groups * l.ssm_state;
             w.qd = w.kd = gn; w.vd = w.od = w.aw = inner;
             w.pw = 2 * inner + 2 * gn + l.n_heads;
             w.conv_c = inner + 2 * gn;
-            w.k_floats = (int64_t)l.n_heads * l.ssm_state * l.v_dim; w.v_floats = std::max<int64_t>(4, (int64_t)(l.conv_taps - 1) * w.conv_c);
+            w.k_floats = (int64_t)l.n_heads * pa_scan_dkp(l.ssm_state) * l.v_dim; w.v_floats = std::max<int64_t>(4, (int64_t)(l.conv_taps - 1) * w.conv_c);
         } else if (w.gen2 && l.conv_taps > 1) { // the last taps - 1 projected rows follow the K rows
             w.conv_c = w.pw;
             w.k_floats = (int64_t)w.kd * d.n_ctx + (int64_t)(l.conv_taps - 1) * w.pw;
@@ -424,6 +424,7 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
         cudaFuncSetAttribute(pa_k_scan<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_scan<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_scan<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_tc_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_tc_gemm<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM) != cudaSuccess) {
         cudaGetLastError();
@@ -859,7 +860,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             const int ff = l.expert_ff;
             float *xout = xo;
             pa_launch_dep(pdl, pa_k_dec_dense_up<ROUND>, dim3(std::min(cdiv(ff, PA_DV_ROWS / 2), (unsigned)(4 * a->n_sm))), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, (const float *)xc,
-                          pend_y, pend_w, (const float *)w.norm_ff, xout, groups, d.norm_eps, (const bf16 *)w.wgate, (const bf16 *)w.wup, a->y, ff, dim, pa_act_of(l));
+                          pend_y, pend_w, (const float *)w.norm_ff, xout, groups, d.norm_eps, (const bf16 *)w.wgate, (const bf16 *)w.wup, a->y, ff, dim, pa_act_of(l), (const bf16 *)nullptr, 0, (float *)nullptr);
             PA_LAUNCH();
             std::swap(xc, xo);
             PaMv mv{};
@@ -905,12 +906,15 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         return linear(a->y, ff, ff, wd, td, dim, out, dim);
     };
     auto scan = [&](const PaScan &sc) -> int {
-        const dim3 grid(cdiv(sc.dv, PA_SC_COLS), (unsigned)sc.H);
+        const dim3 grid(cdiv(sc.dv, pa_scan_cols(sc.dk)), (unsigned)sc.H), blk_s(32 * PA_SC_WARPS);
         const size_t smem = pa_scan_smem(sc.dk);
-        if (sc.dk <= 32) pa_k_scan<1><<<grid, 256, smem, st>>>(sc);
-        else if (sc.dk <= 64) pa_k_scan<2><<<grid, 256, smem, st>>>(sc);
-        else if (sc.dk <= 128) pa_k_scan<4><<<grid, 256, smem, st>>>(sc);
-        else pa_k_scan<8><<<grid, 256, smem, st>>>(sc);
+        switch (pa_scan_il(sc.dk)) {
+        case 1: pa_k_scan<1><<<grid, blk_s, smem, st>>>(sc); break;
+        case 2: pa_k_scan<2><<<grid, blk_s, smem, st>>>(sc); break;
+        case 4: pa_k_scan<4><<<grid, blk_s, smem, st>>>(sc); break;
+        case 8: pa_k_scan<8><<<grid, blk_s, smem, st>>>(sc); break;
+        default: pa_k_scan<16><<<grid, blk_s, smem, st>>>(sc); break;
+        }
         PA_LAUNCH();
         return 0;
     };
@@ -938,9 +942,13 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             float *q = a->qkv;
             if (l.conv_taps > 1) {
                 float *tail = io.kc[li] + (int64_t)w.kd * d.n_ctx;
-                pa_k_short_conv<<<dim3(cdiv(w.pw, 256), bs), 256, 0, st>>>(a->qkv, w.pw, w.conv_w, nullptr, w.pw, l.conv_taps, tail, 0, a->cv, w.pw, io.pos_dev);
-                PA_LAUNCH();
-                pa_k_conv_tail<<<cdiv(w.pw, 256), 256, 0, st>>>(a->qkv, w.pw, w.pw, l.conv_taps, tail, io.pos_dev, bs);
+                if (bs == 1) {
+                    pa_k_conv_step<<<cdiv(w.pw, 256), 256, 0, st>>>(a->qkv, w.conv_w, nullptr, w.pw, l.conv_taps, tail, 0, a->cv, io.pos_dev);
+                } else {
+                    pa_k_short_conv<<<dim3(cdiv(w.pw, 256), bs), 256, 0, st>>>(a->qkv, w.pw, w.conv_w, nullptr, w.pw, l.conv_taps, tail, 0, a->cv, w.pw, io.pos_dev);
+                    PA_LAUNCH();
+                    pa_k_conv_tail<<<cdiv(w.pw, 256), 256, 0, st>>>(a->qkv, w.pw, w.pw, l.conv_taps, tail, io.pos_dev, bs);
+                }
                 PA_LAUNCH();
                 q = a->cv;
             }
@@ -965,23 +973,28 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             sc.q = a->qkv; sc.k = a->qkv + w.qd; sc.v = a->qkv + 2 * w.qd; sc.ldq = sc.ldk = sc.ldv = w.pw; sc.q_gs = sc.k_gs = dq;
             sc.H = sc.G = H; sc.dk = dq; sc.dv = dv; sc.decay = w.decay; sc.S = io.kc[li]; sc.o = a->att; sc.ldo = w.od; sc.pos = io.pos_dev; sc.bs = bs;
             if ((rc = scan(sc))) return rc;
-            pa_k_gate_norm<<<bs, 256, 0, st>>>(a->att, w.od, a->qkv + 2 * w.qd + w.od, w.pw, w.od, H, nullptr, 0, d.norm_eps, a->att, w.od);
+            pa_k_gate_norm<<<dim3((unsigned)H, bs), 256, 0, st>>>(a->att, w.od, a->qkv + 2 * w.qd + w.od, w.pw, w.od, H, nullptr, 0, d.norm_eps, a->att, w.od);
             PA_LAUNCH();
         } else { // PS_MIXER_MAMBA2
             const int inner = w.od, gn = l.ssm_groups * l.ssm_state, T = std::max(1, l.conv_taps);
             float *tail = io.vct[li];
-            pa_k_short_conv<<<dim3(cdiv(w.conv_c, 256), bs), 256, 0, st>>>(a->qkv + inner, w.pw, w.conv_w, w.conv_b, w.conv_c, T, tail, 1, a->cv, w.conv_c, io.pos_dev);
-            PA_LAUNCH();
-            if (T > 1) {
-                pa_k_conv_tail<<<cdiv(w.conv_c, 256), 256, 0, st>>>(a->qkv + inner, w.pw, w.conv_c, T, tail, io.pos_dev, bs);
+            if (bs == 1) {
+                pa_k_conv_step<<<cdiv(w.conv_c, 256), 256, 0, st>>>(a->qkv + inner, w.conv_w, w.conv_b, w.conv_c, T, tail, 1, a->cv, io.pos_dev);
                 PA_LAUNCH();
+            } else {
+                pa_k_short_conv<<<dim3(cdiv(w.conv_c, 256), bs), 256, 0, st>>>(a->qkv + inner, w.pw, w.conv_w, w.conv_b, w.conv_c, T, tail, 1, a->cv, w.conv_c, io.pos_dev);
+                PA_LAUNCH();
+                if (T > 1) {
+                    pa_k_conv_tail<<<cdiv(w.conv_c, 256), 256, 0, st>>>(a->qkv + inner, w.pw, w.conv_c, T, tail, io.pos_dev, bs);
+                    PA_LAUNCH();
+                }
             }
             PaScan sc{};
             sc.q = a->cv + inner + gn; sc.k = a->cv + inner; sc.v = a->cv; sc.ldq = sc.ldk = sc.ldv = w.conv_c; sc.q_gs = sc.k_gs = l.ssm_state;
             sc.H = H; sc.G = l.ssm_groups; sc.dk = l.ssm_state; sc.dv = l.v_dim; sc.dt = a->qkv + 2 * inner + 2 * gn; sc.lddt = w.pw;
             sc.dt_bias = w.dt_bias; sc.a_log = w.a_log; sc.d_skip = w.d_skip; sc.S = io.kc[li]; sc.o = a->att; sc.ldo = inner; sc.pos = io.pos_dev; sc.bs = bs;
             if ((rc = scan(sc))) return rc;
-            pa_k_gate_norm<<<bs, 256, 0, st>>>(a->att, inner, a->qkv, w.pw, inner, l.gate_norm_groups, w.mix_norm, 1, d.norm_eps, a->att, inner);
+            pa_k_gate_norm<<<dim3((unsigned)l.gate_norm_groups, bs), 256, 0, st>>>(a->att, inner, a->qkv, w.pw, inner, l.gate_norm_groups, w.mix_norm, 1, d.norm_eps, a->att, inner);
             PA_LAUNCH();
         }
         if (single) {
@@ -1000,7 +1013,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             const int ff = l.expert_ff;
             if (single) {
                 pa_launch_dep(pdl, pa_k_dec_dense_up<ROUND>, dim3(std::min(cdiv(ff, PA_DV_ROWS / 2), up_cap)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, (const float *)xc, pend_y, pend_w, w_in,
-                              xo, groups, d.norm_eps, (const bf16 *)w.wgate, (const bf16 *)w.wup, a->y, ff, dim, act);
+                              xo, groups, d.norm_eps, (const bf16 *)w.wgate, (const bf16 *)w.wup, a->y, ff, dim, act, (const bf16 *)nullptr, 0, (float *)nullptr);
                 PA_LAUNCH();
                 std::swap(xc, xo);
                 PaMv mv{};
@@ -1017,17 +1030,21 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         const int E = l.n_experts, ff = l.expert_ff, top = l.top_k, sff = l.shared_ff;
         const PaRoute rt = pa_route_of(l);
         if (single) {
-            PaMv mv{}; // the seam, and the router's logits (+ the shared gate's) from the unrounded input
-            seam_mv(mv, w_in);
-            mv.W = nullptr; mv.N = 0; mv.K = dim; mv.Wr = w.router; mv.E = E + (rt.shared_gate ? 1 : 0); mv.z = a->z;
-            if ((rc = dec_mv(mv, 4 * (size_t)dim))) return rc;
-            if (sff > 0) {
-                pa_launch_dep(pdl, pa_k_dec_dense_up<ROUND>, dim3(std::min(cdiv(sff, PA_DV_ROWS / 2), up_cap)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, (const float *)xc, (const float *)nullptr,
-                              (const float *)nullptr, w_in, (float *)nullptr, groups, d.norm_eps, (const bf16 *)w.wsg, (const bf16 *)w.wsu, a->y, sff, dim, act);
+            const int n_rt = E + (rt.shared_gate ? 1 : 0); // the router's rows (+ the shared gate's): logits from the unrounded input
+            if (sff > 0) { // the shared expert's gate | up launch carries the seam and the router's rows
+                pa_launch_dep(pdl, pa_k_dec_dense_up<ROUND>, dim3(std::min(cdiv(sff + n_rt, PA_DV_ROWS / 2), up_cap)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, (const float *)xc, pend_y, pend_w, w_in,
+                              xo, groups, d.norm_eps, (const bf16 *)w.wsg, (const bf16 *)w.wsu, a->y, sff, dim, act, (const bf16 *)w.router, n_rt, a->z);
                 PA_LAUNCH();
+                std::swap(xc, xo);
+                pend_y = pend_w = nullptr;
                 PaMv ms{};
                 ms.x = a->y; ms.W = w.wsd; ms.N = dim; ms.K = sff; ms.y = a->sh;
                 if ((rc = dec_mv(ms, 0))) return rc;
+            } else {
+                PaMv mv{};
+                seam_mv(mv, w_in);
+                mv.W = nullptr; mv.N = 0; mv.K = dim; mv.Wr = w.router; mv.E = n_rt; mv.z = a->z;
+                if ((rc = dec_mv(mv, 4 * (size_t)dim))) return rc;
             }
             pa_k_dec_expert_up<ROUND><<<dim3(std::min(cdiv(ff, PA_DV_ROWS / 2), (unsigned)std::max(1, 4 * a->n_sm / top)), top), PA_DV_THREADS, 4 * (size_t)dim, st>>>(
                 xc, w_in, d.norm_eps, a->z, rt, w.wgate, w.wup, a->y, ff, dim, l.route_on_input, act, a->sel_e, a->sel_w);

@@ -13,7 +13,8 @@
 //                        logarithmic), head mixing, per-block soft-max statistics; with a window the grid starts at the first key in sight
 //   pa_k_dec_pv          soft-max statistics (+ sink logit) per head, weights staged once per CTA, P.V along contiguous V^T rows; many
 //                        heads over one kv head are split over blockIdx.z
-//   pa_k_dec_dense_up    seam in the prologue, gate | up rows of a dense feed-forward, activation
+//   pa_k_dec_dense_up    seam in the prologue, gate | up rows of a dense feed-forward (or of a shared expert, then with the router's
+//                        logits as further rows), activation
 //   pa_k_dec_expert_up   norm + top-k of the router scores in the prologue, gate | up rows of the chosen experts, activation
 //   pa_k_dec_expert_down down rows of the chosen experts summed over the slots + mixer output + residual
 #pragma once
@@ -446,7 +447,8 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_expert_up(const float 
 template <bool ROUND>
 __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_dense_up(const float *__restrict__ x, const float *__restrict__ seam_y, const float *__restrict__ seam_w,
                                                                    const float *__restrict__ norm_w, float *__restrict__ x_out, int groups, float eps, const bf16 *__restrict__ Wg,
-                                                                   const bf16 *__restrict__ Wu, float *__restrict__ y, int ff, int dim, PaAct act) {
+                                                                   const bf16 *__restrict__ Wu, float *__restrict__ y, int ff, int dim, PaAct act,
+                                                                   const bf16 *__restrict__ Wr = nullptr, int E = 0, float *__restrict__ z = nullptr) {
     extern __shared__ __align__(16) float pa_hs[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, rows = PA_DV_ROWS / 2;
     {
@@ -456,8 +458,15 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_dense_up(const float *
     ps_grid_dep_launch();
     ps_grid_dep_wait();
     pa_seam_to_smem(pa_hs, x, seam_y, seam_w, norm_w, x_out, dim, groups, eps);
-    for (int n = blockIdx.x * rows + warp; n < ff; n += gridDim.x * rows) {
+    // E more rows behind the ff rows: a router's logits z[e] = Wr[e] . h from the UNROUNDED input (a shared expert's launch carries them)
+    for (int n = blockIdx.x * rows + warp; n < ff + E; n += gridDim.x * rows) {
         float gsum, usum;
+        if (n >= ff) {
+            const bf16 *wr = Wr + (int64_t)(n - ff) * dim;
+            pa_dot2<false>(wr, wr, pa_hs, dim, 1.0f, lane, gsum, usum);
+            if (lane == 0) z[n - ff] = gsum;
+            continue;
+        }
         pa_dot2<ROUND>(Wg + (int64_t)n * dim, Wu + (int64_t)n * dim, pa_hs, dim, 1.0f, lane, gsum, usum);
         if (lane == 0) y[n] = pa_expert_act(gsum, usum, act);
     }

@@ -7,11 +7,12 @@
 //   pa_k_short_conv      causal convolution over time on every channel, taps newest last, inputs before the batch from the `tail`
 //                        (the last taps - 1 inputs of the sequence), zeros before position 0; optional bias and silu
 //   pa_k_conv_tail       the tail after the batch
+//   pa_k_conv_step       both for a single token
 //   pa_k_qkv_whole_norm  q (all heads) and k RMS-normed as one vector each with weights; K row and V^T column into the cache
 //   pa_k_rope_heads      rotate-half rotation of the first dims of every head, in place, with a scale for the heads from `h_scaled` on
 //   pa_k_scan            S_t = a_t S_(t-1) + k_t (c_t v_t)^T, o_t = S_t^T q_t (+ D v_t): retention (a fixed per head, c = 1) and the
 //                        state-space recurrence (a_t = exp(-exp(A_log) dt_t), c_t = dt_t, dt = softplus(raw + bias)); fp32 state,
-//                        a warp per value column, the state's column in registers, tokens strictly in order (the result does not
+//                        16 entries of a value column per lane in registers, tokens strictly in order (the result does not
 //                        depend on how a prompt was cut)
 //   pa_k_gate_norm       RMS norm in equal parts around a silu gate: (y silu(g)) normed times w, or normed y times silu(g)
 //   pa_k_moe_sum         sum of a token's expert slots (fixed order) plus the gated shared expert
@@ -51,6 +52,24 @@ __global__ void __launch_bounds__(256) pa_k_conv_tail(const float *__restrict__ 
     }
 }
 
+// single token: convolution and tail in one launch, a thread per channel (it alone touches its channel's tail)
+__global__ void __launch_bounds__(256) pa_k_conv_step(const float *__restrict__ u, const float *__restrict__ w, const float *__restrict__ b, int C, int T,
+                                                      float *__restrict__ tail, int act_silu, float *__restrict__ y, const int32_t *__restrict__ pos) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= C) return;
+    const int p0 = pos[0];
+    const float cur = u[c];
+    float acc = b ? b[c] : 0.f;
+    for (int j = 0; j < T - 1; j++) {
+        const float v = p0 - (T - 1) + j >= 0 ? tail[(int64_t)j * C + c] : 0.f;
+        acc = fmaf(w[(int64_t)c * T + j], v, acc);
+        if (j > 0) tail[(int64_t)(j - 1) * C + c] = v;
+    }
+    acc = fmaf(w[(int64_t)c * T + T - 1], cur, acc);
+    if (T > 1) tail[(int64_t)(T - 2) * C + c] = cur;
+    y[c] = act_silu ? pa_silu(acc) : acc;
+}
+
 // one CTA per token; row = [q (qd) | k (kd) | v (vd)]
 __global__ void __launch_bounds__(256) pa_k_qkv_whole_norm(float *__restrict__ qkv, int ld, int qd, int kd, int vd, const float *__restrict__ wq, const float *__restrict__ wk,
                                                            float eps, float *__restrict__ kc, float *__restrict__ vct, int n_ctx, const int32_t *__restrict__ pos) {
@@ -87,8 +106,9 @@ __global__ void __launch_bounds__(256) pa_k_rope_heads(float *__restrict__ v, in
     }
 }
 
-#define PA_SC_TOK 32  // tokens staged per round
-#define PA_SC_COLS 8  // value columns per CTA (a warp each)
+#define PA_SC_TOK 32    // tokens staged per round
+#define PA_SC_WARPS 4
+#define PA_SC_REGS 16   // state entries per lane
 struct PaScan {
     const float *q, *k, *v;   // q[t * ldq + g * q_gs + i], k likewise (i < dk, g = the head's group), v[t * ldv + h * dv + j]
     int ldq, ldk, ldv, q_gs, k_gs;
@@ -97,42 +117,52 @@ struct PaScan {
     const float *dt;          // dt[t * lddt + h] raw step sizes: c_t = softplus(dt + dt_bias[h]), a_t = exp(-exp(a_log[h]) c_t)
     int lddt;
     const float *dt_bias, *a_log, *d_skip; // [H]; d_skip null: no skip term
-    float *S;                 // [H][dk][dv]
+    float *S;                 // [H][dv][dkp]: a value column's state entries lie together, dkp = 16 * pa_scan_il(dk)
     float *o;                 // o[t * ldo + h * dv + j]
     int ldo;
     const int32_t *pos;
     int bs;
 };
-static inline size_t pa_scan_smem(int dk) { return 4 * ((size_t)2 * PA_SC_TOK * dk + (size_t)PA_SC_TOK * (2 * PA_SC_COLS + 2)); }
+// lanes that share a value column: every lane holds PA_SC_REGS state entries of it, so dk <= 16 * IL (IL a power of two, at most 16)
+static inline int pa_scan_il(int dk) { int il = 1; while (il * PA_SC_REGS < dk) il *= 2; return il; }
+static inline int pa_scan_dkp(int dk) { return PA_SC_REGS * pa_scan_il(dk); }
+static inline int pa_scan_cols(int dk) { return 32 / pa_scan_il(dk) * PA_SC_WARPS; } // value columns per CTA
+static inline size_t pa_scan_smem(int dk) { return 4 * ((size_t)2 * PA_SC_TOK * pa_scan_dkp(dk) + (size_t)PA_SC_TOK * (2 * pa_scan_cols(dk) + 2)); }
 
-// grid (dv / PA_SC_COLS, H); R = state entries per lane = ceil(dk / 32)
-template <int R>
-__global__ void __launch_bounds__(256) pa_k_scan(const PaScan a) {
+// grid (dv / columns per CTA, H).  A lane owns entries i = (m * IL + li) * 4 + e (m, e < 4) of one column: k and q come out of shared
+// memory as float4 (lanes of a column read neighbouring float4s, lanes of different columns the same ones), the output is reduced over
+// the IL lanes of a column by log2(IL) shuffles, always in the same order.
+template <int IL>
+__global__ void __launch_bounds__(32 * PA_SC_WARPS) pa_k_scan(const PaScan a) {
     extern __shared__ __align__(16) float sm[];
+    constexpr int CW = 32 / IL, CC = CW * PA_SC_WARPS, DKP = PA_SC_REGS * IL, NT = 32 * PA_SC_WARPS;
     const int dk = a.dk, dv = a.dv;
-    float *qs = sm, *ks = qs + PA_SC_TOK * dk, *vs = ks + PA_SC_TOK * dk, *os = vs + PA_SC_TOK * PA_SC_COLS, *as = os + PA_SC_TOK * PA_SC_COLS, *cs = as + PA_SC_TOK;
-    const int h = blockIdx.y, g = h / (a.H / a.G), j0 = blockIdx.x * PA_SC_COLS, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, j = j0 + warp;
+    float *qs = sm, *ks = qs + PA_SC_TOK * DKP, *vs = ks + PA_SC_TOK * DKP, *os = vs + PA_SC_TOK * CC, *as = os + PA_SC_TOK * CC, *cs = as + PA_SC_TOK;
+    const int h = blockIdx.y, g = h / (a.H / a.G), j0 = blockIdx.x * CC, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int li = lane % IL, col = warp * CW + lane / IL, j = j0 + col;
     const bool fresh = a.pos[0] == 0;
-    float S[R];
+    float S[PA_SC_REGS];
+    float4 *Sg = reinterpret_cast<float4 *>(a.S + ((int64_t)h * dv + min(j, dv - 1)) * DKP) + li;
 #pragma unroll
-    for (int r = 0; r < R; r++) {
-        const int i = lane + 32 * r;
-        S[r] = (!fresh && i < dk && j < dv) ? a.S[((int64_t)h * dk + i) * dv + j] : 0.f;
+    for (int m = 0; m < 4; m++) {
+        const float4 v = (!fresh && j < dv) ? Sg[m * IL] : make_float4(0.f, 0.f, 0.f, 0.f);
+        S[4 * m] = v.x; S[4 * m + 1] = v.y; S[4 * m + 2] = v.z; S[4 * m + 3] = v.w;
     }
     const float rate = a.dt ? expf(a.a_log[h]) : 0.f, bias = a.dt ? a.dt_bias[h] : 0.f, fixed = a.dt ? 0.f : a.decay[h], skip = a.d_skip ? a.d_skip[h] : 0.f;
     for (int t0 = 0; t0 < a.bs; t0 += PA_SC_TOK) {
         const int nt = min(PA_SC_TOK, a.bs - t0);
         __syncthreads(); // the round before has been written out
-        for (int e = tid; e < nt * dk; e += 256) {
-            const int tt = e / dk, i = e % dk;
-            qs[e] = a.q[(int64_t)(t0 + tt) * a.ldq + g * a.q_gs + i];
-            ks[e] = a.k[(int64_t)(t0 + tt) * a.ldk + g * a.k_gs + i];
+        for (int tt = warp; tt < nt; tt += PA_SC_WARPS) {
+            const float *qr = a.q + (int64_t)(t0 + tt) * a.ldq + g * a.q_gs, *kr = a.k + (int64_t)(t0 + tt) * a.ldk + g * a.k_gs;
+#pragma unroll
+            for (int i = lane; i < DKP; i += 32) {
+                qs[tt * DKP + i] = i < dk ? qr[i] : 0.f;
+                ks[tt * DKP + i] = i < dk ? kr[i] : 0.f;
+            }
+            const float *vr = a.v + (int64_t)(t0 + tt) * a.ldv + h * dv + j0;
+            for (int c = lane; c < CC; c += 32) vs[tt * CC + c] = j0 + c < dv ? vr[c] : 0.f;
         }
-        for (int e = tid; e < nt * PA_SC_COLS; e += 256) {
-            const int tt = e / PA_SC_COLS, c = e % PA_SC_COLS;
-            vs[e] = j0 + c < dv ? a.v[(int64_t)(t0 + tt) * a.ldv + h * dv + j0 + c] : 0.f;
-        }
-        for (int tt = tid; tt < nt; tt += 256) {
+        for (int tt = tid; tt < nt; tt += NT) {
             if (a.dt) {
                 const float d = pa_softplus(a.dt[(int64_t)(t0 + tt) * a.lddt + h] + bias);
                 cs[tt] = d;
@@ -144,44 +174,44 @@ __global__ void __launch_bounds__(256) pa_k_scan(const PaScan a) {
         }
         __syncthreads();
         for (int tt = 0; tt < nt; tt++) {
-            const float aa = as[tt], x = vs[tt * PA_SC_COLS + warp], vv = x * cs[tt];
-            float acc = 0.f;
+            const float aa = as[tt], x = vs[tt * CC + col], vv = x * cs[tt];
+            const float4 *k4 = reinterpret_cast<const float4 *>(ks + tt * DKP) + li, *q4 = reinterpret_cast<const float4 *>(qs + tt * DKP) + li;
+            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
 #pragma unroll
-            for (int r = 0; r < R; r++) {
-                const int i = lane + 32 * r;
-                if (i < dk) {
-                    S[r] = fmaf(aa, S[r], ks[tt * dk + i] * vv);
-                    acc = fmaf(S[r], qs[tt * dk + i], acc);
-                }
+            for (int m = 0; m < 4; m++) {
+                const float4 kk = k4[m * IL], qq = q4[m * IL];
+                S[4 * m] = fmaf(aa, S[4 * m], kk.x * vv);         acc0 = fmaf(S[4 * m], qq.x, acc0);
+                S[4 * m + 1] = fmaf(aa, S[4 * m + 1], kk.y * vv); acc1 = fmaf(S[4 * m + 1], qq.y, acc1);
+                S[4 * m + 2] = fmaf(aa, S[4 * m + 2], kk.z * vv); acc2 = fmaf(S[4 * m + 2], qq.z, acc2);
+                S[4 * m + 3] = fmaf(aa, S[4 * m + 3], kk.w * vv); acc3 = fmaf(S[4 * m + 3], qq.w, acc3);
             }
+            float acc = (acc0 + acc1) + (acc2 + acc3);
 #pragma unroll
-            for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (lane == 0) os[tt * PA_SC_COLS + warp] = fmaf(skip, x, acc);
+            for (int o = IL / 2; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (li == 0) os[tt * CC + col] = fmaf(skip, x, acc);
         }
         __syncthreads();
-        for (int e = tid; e < nt * PA_SC_COLS; e += 256) {
-            const int tt = e / PA_SC_COLS, c = e % PA_SC_COLS;
-            if (j0 + c < dv) a.o[(int64_t)(t0 + tt) * a.ldo + h * dv + j0 + c] = os[e];
+        for (int tt = warp; tt < nt; tt += PA_SC_WARPS) {
+            float *orow = a.o + (int64_t)(t0 + tt) * a.ldo + h * dv + j0;
+            for (int c = lane; c < CC; c += 32)
+                if (j0 + c < dv) orow[c] = os[tt * CC + c];
         }
     }
     if (j < dv) {
 #pragma unroll
-        for (int r = 0; r < R; r++) {
-            const int i = lane + 32 * r;
-            if (i < dk) a.S[((int64_t)h * dk + i) * dv + j] = S[r];
-        }
+        for (int m = 0; m < 4; m++) Sg[m * IL] = make_float4(S[4 * m], S[4 * m + 1], S[4 * m + 2], S[4 * m + 3]);
     }
 }
 
-// one CTA per token; `width` entries in `parts` equal parts.  gate_first: out = N(y silu(g)) * w; else out = N(y) * silu(g) (w null: 1)
+// one CTA per (part, token); `width` entries in `parts` equal parts.  gate_first: out = N(y silu(g)) * w; else out = N(y) * silu(g) (w null: 1)
 __global__ void __launch_bounds__(256) pa_k_gate_norm(const float *__restrict__ y, int ldy, const float *__restrict__ gate, int ldg, int width, int parts,
                                                       const float *__restrict__ w, int gate_first, float eps, float *__restrict__ out, int ldo) {
     __shared__ float red[8];
-    const int t = blockIdx.x, ps = width / parts;
+    const int t = blockIdx.y, ps = width / parts;
     const float *yr = y + (int64_t)t * ldy, *gr = gate + (int64_t)t * ldg;
     float *orow = out + (int64_t)t * ldo;
-    for (int p = 0; p < parts; p++) {
-        const int c0 = p * ps;
+    {
+        const int c0 = blockIdx.x * ps;
         float s = 0.f;
         for (int c = threadIdx.x; c < ps; c += 256) {
             const float v = gate_first ? yr[c0 + c] * pa_silu(gr[c0 + c]) : yr[c0 + c];
