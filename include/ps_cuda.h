@@ -234,7 +234,7 @@ int ps_cuda_tp_import(ps_cuda_ctx *ctx, const void *handles, int n);
  *                f_i (1 - ramp_i) with the ramp between the dims whose wavelength fits rope_original positions
  *                rope_fast and rope_slow times, and cos / sin scaled by 0.1 ln(factor) + 1.
  *                chunk > 0: query i sees key j <= i only when floor(i / chunk) = floor(j / chunk) (chunks counted from position 0);
- *                conv_taps > 1: a causal convolution over time on every channel of q, k and v directly after the projection
+ *                conv_taps > 0: a causal convolution over time on every channel of q, k and v directly after the projection
  *                (y_t = sum_j w[c][j] u_(t - taps + 1 + j), zeros before position 0); the last conv_taps - 1 projected rows are
  *                part of the sequence's state; qk_norm = PS_QKNORM_WHOLE: q (all heads at once) and k are RMS-normed as ONE
  *                vector each with the weights q_norm / k_norm.
@@ -304,7 +304,7 @@ typedef struct {
     float   rope_base, rope_factor, rope_fast, rope_slow; /* rope_factor = 0: plain rotation */
     int32_t raw_input;                  /* sequential blocks: no norm on a sublayer's input */
     int32_t chunk;                      /* > 0: attention inside chunks of this many positions only */
-    int32_t conv_taps;                  /* short causal convolution: on q, k, v (attention), on x|B|C (mamba2); 0 or 1 = none */
+    int32_t conv_taps;                  /* short causal convolution: on q, k, v (attention), on x|B|C (mamba2); 0 = none */
     int32_t ssm_state, ssm_groups;      /* mamba2: state size N, groups of heads that share B and C */
     int32_t gate_norm_groups;           /* mamba2: parts of the gated output that are normed separately */
     int32_t act_kind;                   /* enum ps_cuda_act_kind */

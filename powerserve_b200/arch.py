@@ -230,7 +230,7 @@ def _dozotar_describe(cfg: dict, tensors) -> Tuple[List[LayerDesc], dict]:
             d.n_kv_heads, d.qk_dim = m["kv_heads"], m["dim"]
             d.score_scale = m["scale"]
             d.qk_norm = capi.QKNORM_WHOLE
-            d.conv_taps = int(m.get("conv") or 0)
+            d.conv_taps = int(tensors[f"l{i}.mix.q.conv"].shape[1]) if m.get("conv") else 0    # the taps the stored kernel has
             d.rel_buckets = int(tensors[f"l{i}.mix.rel"].shape[0])      # the table's own row count
             d.rel_max_dist = m["bias_max"]
             d.chunk = int((m.get("mask") or {}).get("size", 0))

@@ -275,9 +275,9 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
         (l.block_kind == PS_BLOCK_SEQUENTIAL ? a->has_seq : a->has_par) = true;
         if (l.mixer_kind < PS_MIXER_ATTENTION || l.mixer_kind > PS_MIXER_MAMBA2) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unknown mixer kind %d", i, l.mixer_kind));
         const bool latent = l.mixer_kind == PS_MIXER_LATENT, recur = pa_recurrent(l);
-        w.gen2 = l.block_kind == PS_BLOCK_SEQUENTIAL && (l.raw_input || recur || l.conv_taps > 1 || l.qk_norm == PS_QKNORM_WHOLE || l.chunk > 0 || l.mlp_kind == PS_MLP_ROUTED ||
+        w.gen2 = l.block_kind == PS_BLOCK_SEQUENTIAL && (l.raw_input || recur || l.conv_taps > 0 || l.qk_norm == PS_QKNORM_WHOLE || l.chunk > 0 || l.mlp_kind == PS_MLP_ROUTED ||
                                                          l.rel_buckets > 0 || l.act_kind != PS_ACT_SWISH || l.shared_ff > 0);
-        if (!w.gen2 && (l.raw_input || recur || l.conv_taps > 1 || l.qk_norm == PS_QKNORM_WHOLE || l.chunk > 0 || l.act_kind != PS_ACT_SWISH || l.shared_ff > 0 ||
+        if (!w.gen2 && (l.raw_input || recur || l.conv_taps > 0 || l.qk_norm == PS_QKNORM_WHOLE || l.chunk > 0 || l.act_kind != PS_ACT_SWISH || l.shared_ff > 0 ||
                         l.router_act == PS_ROUTER_SOFTMAX || l.route_groups > 1))
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: raw sublayer inputs, recurrent mixers, convolutions, whole-projection norms, chunked masks, gelu, soft-max / grouped routers and shared experts need a sequential block", i));
         if (w.gen2 && (latent || l.v_mix || l.qk_norm == PS_QKNORM_HEAD || l.proj_bias || l.head_mix || l.head_temp))
@@ -331,7 +331,7 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
             w.pw = 2 * inner + 2 * gn + l.n_heads;
             w.conv_c = inner + 2 * gn;
             w.k_floats = (int64_t)l.n_heads * pa_scan_dkp(l.ssm_state) * l.v_dim; w.v_floats = std::max<int64_t>(4, (int64_t)(l.conv_taps - 1) * w.conv_c);
-        } else if (w.gen2 && l.conv_taps > 1) { // the last taps - 1 projected rows follow the K rows
+        } else if (w.gen2 && l.conv_taps > 0) { // the last taps - 1 projected rows follow the K rows
             w.conv_c = w.pw;
             w.k_floats = (int64_t)w.kd * d.n_ctx + (int64_t)(l.conv_taps - 1) * w.pw;
         }
@@ -551,7 +551,7 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
                 }
             }
             if (w.gen2 && l.qk_norm == PS_QKNORM_WHOLE && ((rc = vec(&w.q_norm, s.q_norm, nq, "q norm", false)) || (rc = vec(&w.k_norm, s.k_norm, nk, "k norm", false)))) return rc;
-            if (w.gen2 && l.mixer_kind == PS_MIXER_ATTENTION && l.conv_taps > 1) {
+            if (w.gen2 && l.mixer_kind == PS_MIXER_ATTENTION && l.conv_taps > 0) {
                 std::vector<float> cw, part;
                 for (auto pr : {std::make_pair(&s.q_conv, nq), std::make_pair(&s.k_conv, nk), std::make_pair(&s.v_conv, nv)}) {
                     if ((rc = small_to_f32(*pr.first, pr.second * l.conv_taps, part, "convolution", err))) return rc;
@@ -940,14 +940,16 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         }
         if (l.mixer_kind == PS_MIXER_ATTENTION) {
             float *q = a->qkv;
-            if (l.conv_taps > 1) {
+            if (l.conv_taps > 0) {
                 float *tail = io.kc[li] + (int64_t)w.kd * d.n_ctx;
                 if (bs == 1) {
                     pa_k_conv_step<<<cdiv(w.pw, 256), 256, 0, st>>>(a->qkv, w.conv_w, nullptr, w.pw, l.conv_taps, tail, 0, a->cv, io.pos_dev);
                 } else {
                     pa_k_short_conv<<<dim3(cdiv(w.pw, 256), bs), 256, 0, st>>>(a->qkv, w.pw, w.conv_w, nullptr, w.pw, l.conv_taps, tail, 0, a->cv, w.pw, io.pos_dev);
-                    PA_LAUNCH();
-                    pa_k_conv_tail<<<cdiv(w.pw, 256), 256, 0, st>>>(a->qkv, w.pw, w.pw, l.conv_taps, tail, io.pos_dev, bs);
+                    if (l.conv_taps > 1) {
+                        PA_LAUNCH();
+                        pa_k_conv_tail<<<cdiv(w.pw, 256), 256, 0, st>>>(a->qkv, w.pw, w.pw, l.conv_taps, tail, io.pos_dev, bs);
+                    }
                 }
                 PA_LAUNCH();
                 q = a->cv;

@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(256) pa_k_rope_heads(float *__restrict__ v, in
     }
 }
 
-#define PA_SC_TOK 32    // tokens staged per round
+#define PA_SC_TOK 32    // tokens staged per round (half as many for the widest states)
 #define PA_SC_WARPS 4
 #define PA_SC_REGS 16   // state entries per lane
 struct PaScan {
@@ -127,17 +127,24 @@ struct PaScan {
 static inline int pa_scan_il(int dk) { int il = 1; while (il * PA_SC_REGS < dk) il *= 2; return il; }
 static inline int pa_scan_dkp(int dk) { return PA_SC_REGS * pa_scan_il(dk); }
 static inline int pa_scan_cols(int dk) { return 32 / pa_scan_il(dk) * PA_SC_WARPS; } // value columns per CTA
-static inline size_t pa_scan_smem(int dk) { return 4 * ((size_t)2 * PA_SC_TOK * pa_scan_dkp(dk) + (size_t)PA_SC_TOK * (2 * pa_scan_cols(dk) + 2)); }
+static inline int pa_scan_tok(int dk) { return pa_scan_il(dk) <= 8 ? PA_SC_TOK : PA_SC_TOK / 2; } // tokens staged per round
+static inline size_t pa_scan_smem(int dk) { return 4 * (size_t)pa_scan_tok(dk) * (2 * (2 * (size_t)pa_scan_dkp(dk) + pa_scan_cols(dk) + 1) + pa_scan_cols(dk) + 2); }
+
+__device__ __forceinline__ void pa_cp_async4(float *dst_smem, const float *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
+}
 
 // grid (dv / columns per CTA, H).  A lane owns entries i = (m * IL + li) * 4 + e (m, e < 4) of one column: k and q come out of shared
 // memory as float4 (lanes of a column read neighbouring float4s, lanes of different columns the same ones), the output is reduced over
-// the IL lanes of a column by log2(IL) shuffles, always in the same order.
+// the IL lanes of a column by log2(IL) shuffles, always in the same order.  The q / k / v rows (and raw step sizes) of a round of tokens
+// arrive by asynchronous 4-byte copies into one of two buffers while the round before is computed.
 template <int IL>
 __global__ void __launch_bounds__(32 * PA_SC_WARPS) pa_k_scan(const PaScan a) {
     extern __shared__ __align__(16) float sm[];
-    constexpr int CW = 32 / IL, CC = CW * PA_SC_WARPS, DKP = PA_SC_REGS * IL, NT = 32 * PA_SC_WARPS;
+    constexpr int CW = 32 / IL, CC = CW * PA_SC_WARPS, DKP = PA_SC_REGS * IL, NT = 32 * PA_SC_WARPS, TOK = IL <= 8 ? PA_SC_TOK : PA_SC_TOK / 2;
+    constexpr int BUF = TOK * (2 * DKP + CC + 1); // floats of one input buffer: q rows, k rows, v entries, raw step sizes
     const int dk = a.dk, dv = a.dv;
-    float *qs = sm, *ks = qs + PA_SC_TOK * DKP, *vs = ks + PA_SC_TOK * DKP, *os = vs + PA_SC_TOK * CC, *as = os + PA_SC_TOK * CC, *cs = as + PA_SC_TOK;
+    float *os = sm + 2 * BUF, *as = os + TOK * CC, *cs = as + TOK;
     const int h = blockIdx.y, g = h / (a.H / a.G), j0 = blockIdx.x * CC, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int li = lane % IL, col = warp * CW + lane / IL, j = j0 + col;
     const bool fresh = a.pos[0] == 0;
@@ -149,22 +156,38 @@ __global__ void __launch_bounds__(32 * PA_SC_WARPS) pa_k_scan(const PaScan a) {
         S[4 * m] = v.x; S[4 * m + 1] = v.y; S[4 * m + 2] = v.z; S[4 * m + 3] = v.w;
     }
     const float rate = a.dt ? expf(a.a_log[h]) : 0.f, bias = a.dt ? a.dt_bias[h] : 0.f, fixed = a.dt ? 0.f : a.decay[h], skip = a.d_skip ? a.d_skip[h] : 0.f;
-    for (int t0 = 0; t0 < a.bs; t0 += PA_SC_TOK) {
-        const int nt = min(PA_SC_TOK, a.bs - t0);
-        __syncthreads(); // the round before has been written out
+    for (int e = tid; e < 2 * BUF; e += NT) sm[e] = 0.f; // what the copies never write (entries beyond dk, columns beyond dv) stays zero
+    __syncthreads();
+    auto fetch = [&](int t0, int buf) {
+        float *qs = sm + buf * BUF, *ks = qs + TOK * DKP, *vs = ks + TOK * DKP, *ds = vs + TOK * CC;
+        const int nt = min(TOK, a.bs - t0);
         for (int tt = warp; tt < nt; tt += PA_SC_WARPS) {
             const float *qr = a.q + (int64_t)(t0 + tt) * a.ldq + g * a.q_gs, *kr = a.k + (int64_t)(t0 + tt) * a.ldk + g * a.k_gs;
-#pragma unroll
-            for (int i = lane; i < DKP; i += 32) {
-                qs[tt * DKP + i] = i < dk ? qr[i] : 0.f;
-                ks[tt * DKP + i] = i < dk ? kr[i] : 0.f;
+            for (int i = lane; i < dk; i += 32) {
+                pa_cp_async4(qs + tt * DKP + i, qr + i);
+                pa_cp_async4(ks + tt * DKP + i, kr + i);
             }
             const float *vr = a.v + (int64_t)(t0 + tt) * a.ldv + h * dv + j0;
-            for (int c = lane; c < CC; c += 32) vs[tt * CC + c] = j0 + c < dv ? vr[c] : 0.f;
+            for (int c = lane; c < CC && j0 + c < dv; c += 32) pa_cp_async4(vs + tt * CC + c, vr + c);
         }
+        if (a.dt)
+            for (int tt = tid; tt < nt; tt += NT) pa_cp_async4(ds + tt, a.dt + (int64_t)(t0 + tt) * a.lddt + h);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(0, 0);
+    for (int t0 = 0, buf = 0; t0 < a.bs; t0 += TOK, buf ^= 1) {
+        const int nt = min(TOK, a.bs - t0);
+        const float *qs = sm + buf * BUF, *ks = qs + TOK * DKP, *vs = ks + TOK * DKP, *ds = vs + TOK * CC;
+        if (t0 + TOK < a.bs) {
+            fetch(t0 + TOK, buf ^ 1); // (every thread left that buffer's round behind the barrier that ended it)
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
         for (int tt = tid; tt < nt; tt += NT) {
             if (a.dt) {
-                const float d = pa_softplus(a.dt[(int64_t)(t0 + tt) * a.lddt + h] + bias);
+                const float d = pa_softplus(ds[tt] + bias);
                 cs[tt] = d;
                 as[tt] = expf(-rate * d);
             } else {

@@ -23,7 +23,7 @@ def test_registry_reads_every_size_from_the_configuration():
               AT(6, 3, 12, 20, chunk=9, conv=4, scale=0.21, bias_max=77.0)]
     layers[1]["mlp"]["router"]["groups"] = {"count": 5, "keep": 2}
     cfg = arch_synth.dozotar_config(60, 99, layers, eps=3e-5)
-    shapes = {"l1.mix.conv": _Shape(33, 5), "l2.mix.rel": _Shape(22, 6)}
+    shapes = {"l1.mix.conv": _Shape(33, 5), "l2.mix.rel": _Shape(22, 6), "l2.mix.q.conv": _Shape(72, 4)}
     descs, top = arch.ARCHITECTURES["Dozotar"][0](cfg, shapes)
     assert top == {"dim": 60, "vocab_size": 99, "norm_eps": 3e-5, "embed_scale": 1.0, "norm_unit_offset": 0, "norm_scalar": 1}
     d = descs[0]

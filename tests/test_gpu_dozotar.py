@@ -105,7 +105,7 @@ def test_state_space_layer_alone(tmp_path, groups, parts, conv):
     alone(tmp_path, MA(4, 6, 9, groups=groups, norm_groups=parts, conv=conv), "state-space-only layer", 2)
 
 
-@pytest.mark.parametrize("conv,chunk", [(3, 11), (0, 16), (5, 40), (2, 1)])
+@pytest.mark.parametrize("conv,chunk", [(3, 11), (0, 16), (5, 40), (2, 1), (1, 7)])
 def test_attention_layer_alone(tmp_path, conv, chunk):
     alone(tmp_path, AT(4, 2, 10, 12, chunk=chunk, conv=conv, bias_max=30.0), "attention-only layer", 3)
 
