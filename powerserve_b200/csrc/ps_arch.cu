@@ -98,6 +98,7 @@ struct PsArch {
     int opt_mv_cap = 0; // > 0: resident mat-vec CTAs per SM (0: two beside overlapping launches, four for long streams or without overlap)
     int opt_prefetch = 1; // 1: a mat-vec CTA requests its first row group into L2 before the dependency wait; 2: every next group too
     int opt_pdl = 1;    // single-token kernels on the main stream are launched with programmatic stream serialisation
+    int opt_scan_nc = 0; // value columns per lane of the recurrence scan (0: chosen by the grid's size)
     bool has_seq = false, has_par = false; // some layer is a sequential / a parallel block
 };
 
@@ -420,11 +421,16 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
         cudaFuncSetAttribute(pa_k_dec_expert_up<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_dec_dense_up<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_dec_dense_up<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
-        cudaFuncSetAttribute(pa_k_scan<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess ||
-        cudaFuncSetAttribute(pa_k_scan<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess ||
-        cudaFuncSetAttribute(pa_k_scan<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess ||
-        cudaFuncSetAttribute(pa_k_scan<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess ||
-        cudaFuncSetAttribute(pa_k_scan<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<8, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<8, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(pa_k_scan<16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_tc_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM) != cudaSuccess ||
         cudaFuncSetAttribute(pa_k_tc_gemm<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PT_SMEM) != cudaSuccess) {
         cudaGetLastError();
@@ -469,6 +475,7 @@ int ps_arch_set_option(PsArch *a, const char *name, int value) {
     if (!strcmp(name, "arch_pdl")) { a->opt_pdl = value; return 1; }
     if (!strcmp(name, "arch_mv_cap")) { a->opt_mv_cap = value; return 1; }
     if (!strcmp(name, "arch_prefetch")) { a->opt_prefetch = value; return 1; }
+    if (!strcmp(name, "arch_scan_nc")) { a->opt_scan_nc = value; return 1; }
     return 0;
 }
 
@@ -906,15 +913,25 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         return linear(a->y, ff, ff, wd, td, dim, out, dim);
     };
     auto scan = [&](const PaScan &sc) -> int {
-        const dim3 grid(cdiv(sc.dv, pa_scan_cols(sc.dk)), (unsigned)sc.H), blk_s(32 * PA_SC_WARPS);
-        const size_t smem = pa_scan_smem(sc.dk);
-        switch (pa_scan_il(sc.dk)) {
-        case 1: pa_k_scan<1><<<grid, blk_s, smem, st>>>(sc); break;
-        case 2: pa_k_scan<2><<<grid, blk_s, smem, st>>>(sc); break;
-        case 4: pa_k_scan<4><<<grid, blk_s, smem, st>>>(sc); break;
-        case 8: pa_k_scan<8><<<grid, blk_s, smem, st>>>(sc); break;
-        default: pa_k_scan<16><<<grid, blk_s, smem, st>>>(sc); break;
+        // columns per lane: two when the grid still gives every SM a CTA (each k / q value read from shared memory then serves two columns)
+        const int il = pa_scan_il(sc.dk);
+        int nc = a->opt_scan_nc;
+        if (nc <= 0) nc = (int64_t)cdiv(sc.dv, pa_scan_cols(sc.dk, 2)) * sc.H >= (bs > 1 ? a->n_sm * 3 / 4 : 4 * a->n_sm) ? 2 : 1;
+        const dim3 grid(cdiv(sc.dv, pa_scan_cols(sc.dk, nc)), (unsigned)sc.H), blk_s(32 * PA_SC_WARPS);
+        const size_t smem = pa_scan_smem(sc.dk, nc);
+#define PA_SCAN_CASE(IL_)                                                              \
+    case IL_:                                                                           \
+        if (nc == 2) pa_k_scan<IL_, 2><<<grid, blk_s, smem, st>>>(sc);                  \
+        else pa_k_scan<IL_, 1><<<grid, blk_s, smem, st>>>(sc);                          \
+        break;
+        switch (il) {
+            PA_SCAN_CASE(1) PA_SCAN_CASE(2) PA_SCAN_CASE(4) PA_SCAN_CASE(8)
+        default:
+            if (nc == 2) pa_k_scan<16, 2><<<grid, blk_s, smem, st>>>(sc);
+            else pa_k_scan<16, 1><<<grid, blk_s, smem, st>>>(sc);
+            break;
         }
+#undef PA_SCAN_CASE
         PA_LAUNCH();
         return 0;
     };

@@ -126,34 +126,41 @@ struct PaScan {
 // lanes that share a value column: every lane holds PA_SC_REGS state entries of it, so dk <= 16 * IL (IL a power of two, at most 16)
 static inline int pa_scan_il(int dk) { int il = 1; while (il * PA_SC_REGS < dk) il *= 2; return il; }
 static inline int pa_scan_dkp(int dk) { return PA_SC_REGS * pa_scan_il(dk); }
-static inline int pa_scan_cols(int dk) { return 32 / pa_scan_il(dk) * PA_SC_WARPS; } // value columns per CTA
+static inline int pa_scan_cols(int dk, int nc) { return 32 / pa_scan_il(dk) * PA_SC_WARPS * nc; } // value columns per CTA, nc per lane
 static inline int pa_scan_tok(int dk) { return pa_scan_il(dk) <= 8 ? PA_SC_TOK : PA_SC_TOK / 2; } // tokens staged per round
-static inline size_t pa_scan_smem(int dk) { return 4 * (size_t)pa_scan_tok(dk) * (2 * (2 * (size_t)pa_scan_dkp(dk) + pa_scan_cols(dk) + 1) + pa_scan_cols(dk) + 2); }
+static inline size_t pa_scan_smem(int dk, int nc) {
+    return 4 * (size_t)pa_scan_tok(dk) * (2 * (2 * (size_t)pa_scan_dkp(dk) + pa_scan_cols(dk, nc) + 1) + pa_scan_cols(dk, nc) + 2);
+}
 
 __device__ __forceinline__ void pa_cp_async4(float *dst_smem, const float *src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
 }
 
-// grid (dv / columns per CTA, H).  A lane owns entries i = (m * IL + li) * 4 + e (m, e < 4) of one column: k and q come out of shared
-// memory as float4 (lanes of a column read neighbouring float4s, lanes of different columns the same ones), the output is reduced over
-// the IL lanes of a column by log2(IL) shuffles, always in the same order.  The q / k / v rows (and raw step sizes) of a round of tokens
-// arrive by asynchronous 4-byte copies into one of two buffers while the round before is computed.
-template <int IL>
+// grid (dv / columns per CTA, H).  A lane owns entries i = (m * IL + li) * 4 + e (m, e < 4) of NC columns: k and q come out of shared
+// memory as float4 (lanes of a column read neighbouring float4s, lanes of different columns the same ones) and serve the lane's NC
+// columns from registers; the output is reduced over the IL lanes of a column by log2(IL) shuffles, always in the same order (the
+// result does not depend on NC).  The q / k / v rows (and raw step sizes) of a round of tokens arrive by asynchronous 4-byte copies
+// into one of two buffers while the round before is computed.
+template <int IL, int NC>
 __global__ void __launch_bounds__(32 * PA_SC_WARPS) pa_k_scan(const PaScan a) {
     extern __shared__ __align__(16) float sm[];
-    constexpr int CW = 32 / IL, CC = CW * PA_SC_WARPS, DKP = PA_SC_REGS * IL, NT = 32 * PA_SC_WARPS, TOK = IL <= 8 ? PA_SC_TOK : PA_SC_TOK / 2;
+    constexpr int CW = 32 / IL, CC = CW * PA_SC_WARPS * NC, DKP = PA_SC_REGS * IL, NT = 32 * PA_SC_WARPS, TOK = IL <= 8 ? PA_SC_TOK : PA_SC_TOK / 2;
     constexpr int BUF = TOK * (2 * DKP + CC + 1); // floats of one input buffer: q rows, k rows, v entries, raw step sizes
     const int dk = a.dk, dv = a.dv;
     float *os = sm + 2 * BUF, *as = os + TOK * CC, *cs = as + TOK;
     const int h = blockIdx.y, g = h / (a.H / a.G), j0 = blockIdx.x * CC, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int li = lane % IL, col = warp * CW + lane / IL, j = j0 + col;
+    const int li = lane % IL, col0 = (warp * NC) * CW + lane / IL; // the lane's columns: col0 + c * CW
     const bool fresh = a.pos[0] == 0;
-    float S[PA_SC_REGS];
-    float4 *Sg = reinterpret_cast<float4 *>(a.S + ((int64_t)h * dv + min(j, dv - 1)) * DKP) + li;
+    float S[NC][PA_SC_REGS];
 #pragma unroll
-    for (int m = 0; m < 4; m++) {
-        const float4 v = (!fresh && j < dv) ? Sg[m * IL] : make_float4(0.f, 0.f, 0.f, 0.f);
-        S[4 * m] = v.x; S[4 * m + 1] = v.y; S[4 * m + 2] = v.z; S[4 * m + 3] = v.w;
+    for (int c = 0; c < NC; c++) {
+        const int j = j0 + col0 + c * CW;
+        const float4 *Sg = reinterpret_cast<const float4 *>(a.S + ((int64_t)h * dv + min(j, dv - 1)) * DKP) + li;
+#pragma unroll
+        for (int m = 0; m < 4; m++) {
+            const float4 v = (!fresh && j < dv) ? Sg[m * IL] : make_float4(0.f, 0.f, 0.f, 0.f);
+            S[c][4 * m] = v.x; S[c][4 * m + 1] = v.y; S[c][4 * m + 2] = v.z; S[c][4 * m + 3] = v.w;
+        }
     }
     const float rate = a.dt ? expf(a.a_log[h]) : 0.f, bias = a.dt ? a.dt_bias[h] : 0.f, fixed = a.dt ? 0.f : a.decay[h], skip = a.d_skip ? a.d_skip[h] : 0.f;
     for (int e = tid; e < 2 * BUF; e += NT) sm[e] = 0.f; // what the copies never write (entries beyond dk, columns beyond dv) stays zero
@@ -197,21 +204,33 @@ __global__ void __launch_bounds__(32 * PA_SC_WARPS) pa_k_scan(const PaScan a) {
         }
         __syncthreads();
         for (int tt = 0; tt < nt; tt++) {
-            const float aa = as[tt], x = vs[tt * CC + col], vv = x * cs[tt];
+            const float aa = as[tt], ct = cs[tt];
+            float x[NC], vv[NC], acc[NC][4];
+#pragma unroll
+            for (int c = 0; c < NC; c++) {
+                x[c] = vs[tt * CC + col0 + c * CW];
+                vv[c] = x[c] * ct;
+                acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
+            }
             const float4 *k4 = reinterpret_cast<const float4 *>(ks + tt * DKP) + li, *q4 = reinterpret_cast<const float4 *>(qs + tt * DKP) + li;
-            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
 #pragma unroll
             for (int m = 0; m < 4; m++) {
                 const float4 kk = k4[m * IL], qq = q4[m * IL];
-                S[4 * m] = fmaf(aa, S[4 * m], kk.x * vv);         acc0 = fmaf(S[4 * m], qq.x, acc0);
-                S[4 * m + 1] = fmaf(aa, S[4 * m + 1], kk.y * vv); acc1 = fmaf(S[4 * m + 1], qq.y, acc1);
-                S[4 * m + 2] = fmaf(aa, S[4 * m + 2], kk.z * vv); acc2 = fmaf(S[4 * m + 2], qq.z, acc2);
-                S[4 * m + 3] = fmaf(aa, S[4 * m + 3], kk.w * vv); acc3 = fmaf(S[4 * m + 3], qq.w, acc3);
-            }
-            float acc = (acc0 + acc1) + (acc2 + acc3);
 #pragma unroll
-            for (int o = IL / 2; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (li == 0) os[tt * CC + col] = fmaf(skip, x, acc);
+                for (int c = 0; c < NC; c++) {
+                    S[c][4 * m] = fmaf(aa, S[c][4 * m], kk.x * vv[c]);         acc[c][0] = fmaf(S[c][4 * m], qq.x, acc[c][0]);
+                    S[c][4 * m + 1] = fmaf(aa, S[c][4 * m + 1], kk.y * vv[c]); acc[c][1] = fmaf(S[c][4 * m + 1], qq.y, acc[c][1]);
+                    S[c][4 * m + 2] = fmaf(aa, S[c][4 * m + 2], kk.z * vv[c]); acc[c][2] = fmaf(S[c][4 * m + 2], qq.z, acc[c][2]);
+                    S[c][4 * m + 3] = fmaf(aa, S[c][4 * m + 3], kk.w * vv[c]); acc[c][3] = fmaf(S[c][4 * m + 3], qq.w, acc[c][3]);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < NC; c++) {
+                float r = (acc[c][0] + acc[c][1]) + (acc[c][2] + acc[c][3]);
+#pragma unroll
+                for (int o = IL / 2; o; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+                if (li == 0) os[tt * CC + col0 + c * CW] = fmaf(skip, x[c], r);
+            }
         }
         __syncthreads();
         for (int tt = warp; tt < nt; tt += PA_SC_WARPS) {
@@ -220,9 +239,13 @@ __global__ void __launch_bounds__(32 * PA_SC_WARPS) pa_k_scan(const PaScan a) {
                 if (j0 + c < dv) orow[c] = os[tt * CC + c];
         }
     }
-    if (j < dv) {
 #pragma unroll
-        for (int m = 0; m < 4; m++) Sg[m * IL] = make_float4(S[4 * m], S[4 * m + 1], S[4 * m + 2], S[4 * m + 3]);
+    for (int c = 0; c < NC; c++) {
+        const int j = j0 + col0 + c * CW;
+        if (j >= dv) continue;
+        float4 *Sg = reinterpret_cast<float4 *>(a.S + ((int64_t)h * dv + j) * DKP) + li;
+#pragma unroll
+        for (int m = 0; m < 4; m++) Sg[m * IL] = make_float4(S[c][4 * m], S[c][4 * m + 1], S[c][4 * m + 2], S[c][4 * m + 3]);
     }
 }
 
