@@ -986,7 +986,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         } else if (l.mixer_kind == PS_MIXER_RETENTION) {
             const int dq = l.qk_dim, dv = l.v_dim;
             const PaRope rope{w.rope_freq, l.rope_dims, 1.0f};
-            pa_k_rope_heads<<<bs, 256, 0, st>>>(a->qkv, w.pw, 2 * H, dq, rope, H, 1.0f / sqrtf((float)dq), io.pos_dev); // q | k rotated, k scaled
+            pa_k_rope_heads<<<dim3(cdiv(2 * H * dq, 256), bs), 256, 0, st>>>(a->qkv, w.pw, 2 * H, dq, rope, H, 1.0f / sqrtf((float)dq), io.pos_dev); // q | k rotated, k scaled
             PA_LAUNCH();
             PaScan sc{};
             sc.q = a->qkv; sc.k = a->qkv + w.qd; sc.v = a->qkv + 2 * w.qd; sc.ldq = sc.ldk = sc.ldv = w.pw; sc.q_gs = sc.k_gs = dq;

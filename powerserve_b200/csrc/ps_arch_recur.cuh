@@ -87,11 +87,11 @@ __global__ void __launch_bounds__(256) pa_k_qkv_whole_norm(float *__restrict__ q
     for (int c = threadIdx.x; c < vd; c += 256) vct[(int64_t)c * n_ctx + p] = row[qd + kd + c];
 }
 
-// one CTA per token; n_heads heads of hd entries from v[t * ld] on; heads h >= h_scaled are multiplied by `scale` after the rotation
+// grid (entries / 256, tokens); n_heads heads of hd entries from v[t * ld] on; heads h >= h_scaled are multiplied by `scale` after the rotation
 __global__ void __launch_bounds__(256) pa_k_rope_heads(float *__restrict__ v, int ld, int n_heads, int hd, PaRope rope, int h_scaled, float scale, const int32_t *__restrict__ pos) {
-    const int t = blockIdx.x, p = pos[t], half = rope.dims >> 1;
+    const int t = blockIdx.y, p = pos[t], half = rope.dims >> 1;
     float *row = v + (int64_t)t * ld;
-    for (int e = threadIdx.x; e < n_heads * hd; e += 256) {
+    for (int e = blockIdx.x * 256 + threadIdx.x; e < n_heads * hd; e += gridDim.x * 256) {
         const int hh = e / hd, c = e % hd;
         const float sc = hh >= h_scaled ? scale : 1.0f;
         float *x = row + hh * hd;
