@@ -285,7 +285,7 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: latent attention, value blending, per-head unit norms, projection biases and head mixing are not combined with this layer's other mechanisms", i));
         if (w.gen2 && l.mlp_kind == PS_MLP_ROUTED && !l.raw_input && d.norm_groups > 1)
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: routed experts behind a group norm", i));
-        if (l.chunk < 0 || l.conv_taps < 0 || l.conv_taps > 16 || l.act_kind < PS_ACT_SWISH || l.act_kind > PS_ACT_GELU_TANH || l.shared_ff < 0)
+        if (l.chunk < 0 || l.conv_taps < 0 || l.conv_taps > 64 || l.act_kind < PS_ACT_SWISH || l.act_kind > PS_ACT_GELU_TANH || l.shared_ff < 0)
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: chunk %d, %d convolution taps, activation %d, shared expert of %d rows", i, l.chunk, l.conv_taps, l.act_kind, l.shared_ff));
         if (l.mixer_kind == PS_MIXER_RETENTION && (l.rope_dims < 0 || l.rope_dims > l.qk_dim || (l.rope_dims & 1) || (l.rope_dims > 0 && !(l.rope_base > 0.f)) || l.qk_dim > 256 || l.rope_factor != 0.f))
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: retention with heads of %d of which %d rotate (at most 256)", i, l.qk_dim, l.rope_dims));
