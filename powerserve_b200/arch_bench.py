@@ -217,7 +217,7 @@ def run_size_dozotar(name, prompt_len, steps, warmup, seed, chunk):
     for i, k in enumerate(kinds):
         mlp = dict(ff=2 * ff) if i == 0 else moe
         if k == "r":
-            layers.append(arch_synth.dozotar_retention_layer(RH, rd, rv, rot_base=1e6, **mlp))
+            layers.append(arch_synth.dozotar_retention_layer(RH, rd, rv, rot_base=5e5, **mlp))
         elif k == "m":
             layers.append(arch_synth.dozotar_mamba2_layer(MH, mp, N, groups=mg, norm_groups=mg, conv=4, **mlp))
         else:

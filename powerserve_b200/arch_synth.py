@@ -175,7 +175,7 @@ def dozotar_mamba2_layer(heads: int, vdim: int, state: int, *, groups: int = 1, 
     return {"type": "mamba2", "mixer": mixer, "mlp": _dozotar_mlp(**mlp)}
 
 
-def dozotar_config(width: int, vocab: int, layers: List[dict], *, eps: float = 1e-6) -> dict:
+def dozotar_config(width: int, vocab: int, layers: List[dict], *, eps: float = 1e-5) -> dict:
     return {"architecture": "Dozotar", "layers": layers, "norm": {"eps": eps}, "vocab": vocab, "width": width}
 
 

@@ -29,7 +29,7 @@
 // two rows at once: s0 += w0 . f(x), s1 += w1 . f(x) with f = bfloat16 rounding (ROUND) of x * xscale, or identity
 template <bool ROUND>
 __device__ __forceinline__ void pa_dot2(const bf16 *__restrict__ w0, const bf16 *__restrict__ w1, const float *x, int K, float xscale, int lane, float &s0, float &s1,
-                                        int k_begin = 0, int k_end = -1) {
+                                        int k_begin, int k_end) {
     s0 = s1 = 0.f;
     if (k_end < 0) k_end = K;
     if ((K & 7) == 0 && (k_begin & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) { // (a head's slice of x may start anywhere)

@@ -48,6 +48,11 @@ template <bool ROUND> __device__ __forceinline__ float pa_rnd(float v) {
 __device__ __forceinline__ float pa_ld(const bf16 *p) { return __bfloat162float(*p); }
 __device__ __forceinline__ float pa_ld(const float *p) { return *p; }
 
+// two weight rows against one fp32 vector, reduced over the warp (defined with the single-token kernels, ps_arch_decode.cuh)
+template <bool ROUND>
+__device__ __forceinline__ void pa_dot2(const bf16 *__restrict__ w0, const bf16 *__restrict__ w1, const float *x, int K, float xscale, int lane, float &s0, float &s1,
+                                        int k_begin = 0, int k_end = -1);
+
 // ---------------------------------------------------------------------------------------------------------------- tile core
 // acc[i][j] += sum_k A(ty * 4 + i, k) * B(tx * 4 + j, k) for the CTA's 64 x 64 tile.  Every thread stages 4 k-values of ONE A
 // row and ONE B row per step: `arow` / `brow` point at row (tid >> 2) of the tile (null = outside: zeros).
@@ -369,13 +374,12 @@ __global__ void __launch_bounds__(256) pa_k_router(const float *__restrict__ h, 
     __shared__ int se[PA_MAX_EXPERTS];
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float *hr = h + (int64_t)t * dim;
-    for (int e = warp; e < r.E + (r.shared_gate ? 1 : 0); e += 8) {
-        const bf16 *wr = Wr + (int64_t)e * dim;
-        float s = 0.f;
-        for (int k = lane; k < dim; k += 32) s = fmaf(__bfloat162float(wr[k]), hr[k], s);
-#pragma unroll
-        for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        if (lane == 0) zs[e] = s;
+    const int n_rows = r.E + (r.shared_gate ? 1 : 0);
+    for (int e = 2 * warp; e < n_rows; e += 16) { // a warp takes two rows at a time (16-byte loads where the width allows)
+        const int e1 = min(e + 1, n_rows - 1);
+        float s0, s1;
+        pa_dot2<false>(Wr + (int64_t)e * dim, Wr + (int64_t)e1 * dim, hr, dim, 1.0f, lane, s0, s1);
+        if (lane == 0) { zs[e] = s0; zs[e1] = s1; }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
