@@ -259,7 +259,29 @@ int ps_cuda_tp_import(ps_cuda_ctx *ctx, const void *handles, int n);
  *                shared_ff > 0: one more expert of that many rows runs for every token and is added, times
  *                sigmoid(shared_sg . z) when shared_gate = 1.
  *   raw_input  - sequential blocks: the sublayers read the residual stream itself (no norm on the way in).
- *   norm       - RMS norm with eps inside the root; norm_unit_offset = 1: the stored weight is around zero (1 + w);
+ *   values from keys - v_is_k = 1: there is no W_v; a position's value row is its projected key row as it leaves the projection
+ *                (before any q / k norm); v_dim = qk_dim.
+ *   pooled window - pool > 0 (with window > 0): beside the window's tokens a query at position i sees one key and value for every block
+ *                of `pool` positions that lies wholly before its window (block b = positions b pool .. b pool + pool - 1, seen when
+ *                b pool + pool - 1 <= i - window): the means of the block's cached key rows and value rows.  Tokens that have left the
+ *                window and whose block is not complete yet are not seen.  Tokens and blocks share one soft-max; a block's score
+ *                carries no distance term.  The cache set keeps the means behind the layer's K rows and V^T rows.
+ *   linear distance bias - lin_bias = 1: score -= lin[h] * (i - j).
+ *   output gate - out_gate = 1: the concatenated heads are multiplied by sigmoid(W_g h) (tensor g, [H * v_dim][dim]) before the
+ *                output projection; W_g reads the mixer's input.
+ *   side mixer - side_kind = PS_MIXER_MINGRU: a gated recurrence beside the attention, reading the same input: z = sigmoid(W_z h + b_z),
+ *                u = W_x h + b_x, candidate c = u + 1/2 (u >= 0) or sigmoid(u) (u < 0), S_t = (1 - z) S_(t-1) + z c element by
+ *                element over side_width channels (fp32, zero at position 0), output W_so (S_t silu(W_sg h)).  The layer's mixer
+ *                output is mix_scale * attention + side_scale * side (one product over the concatenated inputs).
+ *   interleaved rotation - rope_interleaved = 1: the rotation pairs dims (2i, 2i + 1) instead of (i, i + rope_dims / 2).
+ *   ungated ff - mlp_ungated = 1 (PS_MLP_DENSE): out = W_down act(W_up h), act the one-argument form of act_kind; PS_ACT_XIELU with the
+ *                two numbers p, q of tensor act: z > 0: softplus(p) z^2 + z / 2; z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2.
+ *   layer runs - the descriptor's layer list is the list of layer RUNS: share_weights = j + 1 makes a run use the weights of run j
+ *                (same sizes; its own cache and state), so a group of layers can be passed through several times.  pass_embed = 1
+ *                adds the embedding output (the residual stream as it was before the first run) to the stream before the run,
+ *                pass_step = r + 1 adds row r of the model's pass_steps table [n_pass_steps][dim].
+ *   norm       - RMS norm with eps inside the root; norm_kind = PS_NORM_LAYER: the mean is taken off first and the divisor is
+ *                sqrt(variance + eps) (a weight, no bias); norm_unit_offset = 1: the stored weight is around zero (1 + w);
  *                norm_groups > 1: the vector is cut into that many equal parts, each divided by its own root mean square;
  *                norm_scalar = 1: every norm's weight is a single number for all coordinates.
  * The context made by ps_cuda_create_arch is an ordinary ps_cuda_ctx: ps_cuda_forward, ps_cuda_decode_greedy,
@@ -270,13 +292,14 @@ int ps_cuda_tp_import(ps_cuda_ctx *ctx, const void *handles, int n);
  * compute = PS_COMPUTE_BF16: matrix products take bfloat16 operands and accumulate in fp32; the residual stream, norms,
  * attention scores / weights, routers and the cache stay fp32.  PS_COMPUTE_F32: every product in true fp32 (FMA). */
 enum ps_cuda_compute { PS_COMPUTE_BF16 = 0, PS_COMPUTE_F32 = 1 };
-enum ps_cuda_mixer_kind { PS_MIXER_ATTENTION = 1, PS_MIXER_LATENT = 2, PS_MIXER_RETENTION = 3, PS_MIXER_MAMBA2 = 4 };
+enum ps_cuda_mixer_kind { PS_MIXER_ATTENTION = 1, PS_MIXER_LATENT = 2, PS_MIXER_RETENTION = 3, PS_MIXER_MAMBA2 = 4, PS_MIXER_MINGRU = 5 /* side mixer only */ };
 enum ps_cuda_mlp_kind { PS_MLP_NONE = 0, PS_MLP_ROUTED = 1, PS_MLP_DENSE = 2 };
 enum ps_cuda_block_kind { PS_BLOCK_PARALLEL = 0, PS_BLOCK_SEQUENTIAL = 1 };
 enum ps_cuda_sink_kind { PS_SINK_NONE = 0, PS_SINK_ZERO = 1, PS_SINK_LEARNED = 2 };
 enum ps_cuda_vmix_kind { PS_VMIX_NONE = 0, PS_VMIX_SOURCE = 1, PS_VMIX_BLEND = 2 };
 enum ps_cuda_qknorm_kind { PS_QKNORM_NONE = 0, PS_QKNORM_HEAD = 1, PS_QKNORM_WHOLE = 2 };
-enum ps_cuda_act_kind { PS_ACT_SWISH = 0, PS_ACT_GELU_TANH = 1 };
+enum ps_cuda_act_kind { PS_ACT_SWISH = 0, PS_ACT_GELU_TANH = 1, PS_ACT_XIELU = 2 };
+enum ps_cuda_norm_kind { PS_NORM_RMS = 0, PS_NORM_LAYER = 1 };
 enum ps_cuda_router_act { PS_ROUTER_SIGMOID = 1, PS_ROUTER_SOFTMAX = 2 };
 
 typedef struct {
@@ -311,6 +334,16 @@ typedef struct {
     int32_t route_groups, route_keep;   /* group-limited routing (route_groups <= 1: every expert can be chosen) */
     float   route_renorm_eps;           /* added to the sum of the chosen scores before the division */
     int32_t shared_ff, shared_gate;     /* rows of the shared expert (0 = none); 1 = its output is scaled by sigmoid(shared_sg . z) */
+    int32_t v_is_k;                     /* the value rows are the projected key rows (no W_v) */
+    int32_t pool;                       /* > 0: mean key / value per block of this many positions wholly before the window */
+    int32_t lin_bias;                   /* score -= lin[h] * distance */
+    int32_t out_gate;                   /* heads' outputs times sigmoid(W_g h) before the output projection */
+    int32_t side_kind, side_width;      /* a second mixer beside the attention (0 = none, PS_MIXER_MINGRU) and its channels */
+    float   mix_scale, side_scale;      /* mixer output = mix_scale * attention + side_scale * side (used when side_kind != 0) */
+    int32_t rope_interleaved;           /* rotation pairs (2i, 2i + 1) */
+    int32_t mlp_ungated;                /* dense feed-forward without a gate: down(act(up h)) */
+    int32_t share_weights;              /* j + 1: this run uses the weights of run j */
+    int32_t pass_embed, pass_step;      /* before the run: add the embedding output; add row pass_step - 1 of pass_steps */
 } ps_cuda_layer_desc;
 
 typedef struct {
@@ -322,6 +355,8 @@ typedef struct {
     const ps_cuda_layer_desc *layers;   /* n_layers entries */
     int32_t norm_groups;                /* 0 or 1: one group */
     int32_t norm_scalar;                /* the norms' weights are single numbers */
+    int32_t norm_kind;                  /* enum ps_cuda_norm_kind: the block norms and the final norm */
+    int32_t n_pass_steps;               /* rows of the pass_steps table */
 } ps_cuda_arch_desc;
 
 /* matrices [out][in] in bfloat16; vectors and the small tables in bfloat16 or fp32 */
@@ -336,11 +371,14 @@ typedef struct {
     ps_cuda_tensor g, decay;            /* retention: gate projection [H * v_dim][dim]; decays [H] */
     ps_cuda_tensor w_in, conv_w, conv_b, dt_bias, a_log, d_skip, mix_norm; /* mamba2 */
     ps_cuda_tensor shared_gate, shared_up, shared_down, shared_sg; /* shared expert */
+    ps_cuda_tensor lin, act;            /* linear distance-bias slopes [H]; the activation's numbers [2] */
+    ps_cuda_tensor side_z, side_z_bias, side_x, side_x_bias, side_g, side_o; /* side mixer: [W][dim], [W], [W][dim], [W], [W][dim], [dim][W] */
 } ps_cuda_arch_layer_weights;
 
 typedef struct {
     ps_cuda_tensor embed, final_norm, head;
-    const ps_cuda_arch_layer_weights *layers;
+    const ps_cuda_arch_layer_weights *layers; /* one entry per run; the entries of runs that share another run's weights are not read */
+    ps_cuda_tensor pass_steps;          /* [n_pass_steps][dim] */
 } ps_cuda_arch_weights;
 
 int ps_cuda_create_arch(ps_cuda_ctx **out, int device, const ps_cuda_arch_desc *desc);

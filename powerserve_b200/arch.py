@@ -40,7 +40,8 @@ class LayerListModel(capi.CudaModel):
         layers, top = describe(cfg, self.tensors)
         self._layer_descs = (LayerDesc * len(layers))(*layers)
         self.desc = ArchDesc(top["dim"], top["vocab_size"], len(layers), int(n_ctx), int(max_batch), top["norm_eps"], top["embed_scale"],
-                             top["norm_unit_offset"], compute, self._layer_descs, int(top.get("norm_groups", 1)), int(top.get("norm_scalar", 0)))
+                             top["norm_unit_offset"], compute, self._layer_descs, int(top.get("norm_groups", 1)), int(top.get("norm_scalar", 0)),
+                             int(top.get("norm_kind", 0)), int(top.get("n_pass_steps", 0)))
         self.vocab = self.desc.vocab_size
         self.be = capi.CudaBackend(self.desc, device)
 
@@ -69,7 +70,7 @@ class LayerListModel(capi.CudaModel):
                     self._keep.append(arr)
                     setattr(lw, f, arr)
             self._lw[i] = lw
-        self._w = ArchWeights(T(names["embed"]), T(names["final_norm"]), T(names["head"]), self._lw)
+        self._w = ArchWeights(T(names["embed"]), T(names["final_norm"]), T(names["head"]), self._lw, T(names.get("pass_steps")))
         self.be._ck(self.be.L.ps_cuda_bind_arch(self.be.h, C.byref(self._w)))
 
     def layer_tap(self, layer: int, bs: int):
@@ -300,8 +301,123 @@ def _dozotar_tensor_names(cfg: dict) -> dict:
     return out
 
 
+# ------------------------------------------------------------------------------------------------------------ Pidenex
+# Decoder-only; every layer is a sequential block with a layer norm (mean removed, weight, no bias) on the way into AND out of every
+# sublayer.  config "loop" runs the layers start .. stop - 1 `times` times with the same weights - every pass with a cache / state of
+# its own - then the rest; before every pass but the first the embedding output joins the stream, before every pass row t of "loop.step".
+# The descriptor therefore lists layer RUNS; a repeated run names the run whose weights it uses.  Three mixers, chosen by "type":
+#   "attention"         grouped-query, no rotation, the values ARE the projected keys; a window of mask.size tokens plus one mean key /
+#                       value per block of mask.pool tokens that lies wholly before the window.
+#   "parallel"          two mixers on the same input, summed with left_scale / right_scale: "left" an attention whose values are the
+#                       un-normed keys, q / k normed over the whole projection with weights, a penalty slope_h (i - j) with
+#                       slope_h = 2^(-8 (h + 1) / H), a window, a sigmoid output gate; "right" a minGRU recurrence.
+#   "latent_attention"  queries through a normed latent, keys / values from a shared normed latent plus one rotated key part common to
+#                       all heads; rotation in neighbouring pairs (2i, 2i + 1); a window.
+# Feed-forward: down(xIELU(up h)) with the activation's two numbers per layer.  Embedding scaled; final layer norm; untied head.
+def _pidenex_runs(cfg: dict) -> List[Tuple[int, Optional[int]]]:
+    """(layer, number of the pass that this run opens or None) in execution order"""
+    n = len(cfg["layers"])
+    lp = cfg.get("loop") or {}
+    a, b, times = int(lp.get("start", 0)), int(lp.get("stop", 0)), int(lp.get("times", 1))
+    if not (0 <= a <= b <= n) or times < 1:
+        raise capi.PsCudaError(f"Pidenex: loop {lp!r} does not fit {n} layers")
+    runs: List[Tuple[int, Optional[int]]] = [(i, None) for i in range(a)]
+    if b > a:
+        for t in range(times):
+            runs += [(i, t if i == a else None) for i in range(a, b)]
+    return runs + [(i, None) for i in range(b, n)]
+
+
+def _pidenex_attention(d: LayerDesc, m: dict) -> None:
+    d.mixer_kind = capi.MIXER_ATTENTION
+    d.n_heads, d.n_kv_heads, d.qk_dim, d.v_dim = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    d.score_scale = m["scale"]
+    d.v_is_k = 1
+    mask = m.get("mask") or {}
+    d.window, d.pool = int(mask.get("size", 0)), int(mask.get("pool", 0))
+
+
+def _pidenex_describe(cfg: dict, tensors) -> Tuple[List[LayerDesc], dict]:
+    layers = []
+    first_run: Dict[int, int] = {}
+    for r, (i, t) in enumerate(_pidenex_runs(cfg)):
+        l = cfg["layers"][i]
+        m = l["mixer"]
+        d = LayerDesc()
+        d.block_kind, d.post_norm = capi.BLOCK_SEQUENTIAL, 1
+        if l["type"] == "attention":
+            _pidenex_attention(d, m)
+        elif l["type"] == "parallel":
+            _pidenex_attention(d, m["left"])
+            d.qk_norm, d.lin_bias, d.out_gate = capi.QKNORM_WHOLE, 1, 1
+            d.side_kind, d.side_width = capi.MIXER_MINGRU, int(m["right"]["width"])
+            d.mix_scale, d.side_scale = float(m["left_scale"]), float(m["right_scale"])
+        elif l["type"] == "latent_attention":
+            d.mixer_kind = capi.MIXER_LATENT
+            d.n_heads, d.n_kv_heads, d.qk_dim, d.v_dim = m["heads"], 1, m["dim"], m["vdim"]
+            d.score_scale = m["scale"]
+            d.q_rank, d.kv_rank, d.rot_dim = m["q_rank"], m["kv_rank"], m["rot_dim"]
+            rot = m.get("rot") or {}
+            d.rope_dims, d.rope_base, d.rope_interleaved = int(rot.get("dims", d.rot_dim)), float(rot.get("base", 10000.0)), 1
+            d.window = int((m.get("mask") or {}).get("size", 0))
+        else:
+            raise capi.PsCudaError(f"Pidenex layer {i}: unknown mixer type {l['type']!r}")
+        mlp = l.get("mlp")
+        if mlp is None:
+            d.mlp_kind = capi.MLP_NONE
+        elif mlp.get("kind") == "dense":
+            d.mlp_kind, d.expert_ff, d.mlp_ungated, d.act_kind = capi.MLP_DENSE, mlp["ff"], 1, capi.ACT_XIELU
+        else:
+            raise capi.PsCudaError(f"Pidenex layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+        if i in first_run:
+            d.share_weights = first_run[i] + 1
+        else:
+            first_run[i] = r
+        if t is not None:
+            d.pass_step = t + 1
+            d.pass_embed = 1 if t > 0 else 0
+        layers.append(d)
+    lp = cfg.get("loop") or {}
+    looped = int(lp.get("stop", 0)) > int(lp.get("start", 0))
+    top = {"dim": cfg["width"], "vocab_size": cfg["vocab"], "norm_eps": cfg["norm"]["eps"], "embed_scale": cfg["embedding"]["scale"], "norm_unit_offset": 0,
+           "norm_kind": capi.NORM_LAYER, "n_pass_steps": int(lp.get("times", 1)) if looped else 0}
+    return layers, top
+
+
+def _pidenex_tensor_names(cfg: dict) -> dict:
+    out = {"embed": "embed", "final_norm": "final.norm", "head": "head", "layers": []}
+    lp = cfg.get("loop") or {}
+    if int(lp.get("stop", 0)) > int(lp.get("start", 0)):
+        out["pass_steps"] = "loop.step"
+    seen = set()
+    for i, _ in _pidenex_runs(cfg):
+        if i in seen:                 # a repeated run: the weights of its first run
+            out["layers"].append({})
+            continue
+        seen.add(i)
+        l = cfg["layers"][i]
+        p = f"l{i}."
+        n = {"norm": p + "norm1", "norm_mix_out": p + "norm1b"}
+        if l["type"] == "attention":
+            n.update({"q": p + "mix.q", "k": p + "mix.k", "o": p + "mix.o"})
+        elif l["type"] == "parallel":
+            a, b = p + "mix.left.", p + "mix.right."
+            H = l["mixer"]["left"]["heads"]
+            n.update({"q": a + "q", "k": a + "k", "q_norm": a + "q.norm", "k_norm": a + "k.norm", "g": a + "g", "o": a + "o",
+                      "lin": np.asarray([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], np.float32),
+                      "side_z": b + "z", "side_z_bias": b + "z.b", "side_x": b + "x", "side_x_bias": b + "x.b", "side_g": b + "g", "side_o": b + "o"})
+        else:
+            n.update({"dq": p + "mix.dq", "dq_norm": p + "mix.dq.norm", "uq": p + "mix.uq", "dkv": p + "mix.dkv", "dkv_norm": p + "mix.dkv.norm",
+                      "uk": p + "mix.uk", "uv": p + "mix.uv", "o": p + "mix.o"})
+        if l.get("mlp") is not None:
+            n.update({"norm_ff": p + "norm2", "norm_ff_out": p + "norm2b", "up": [p + "mlp.up"], "down": [p + "mlp.down"], "act": p + "mlp.act"})
+        out["layers"].append(n)
+    return out
+
+
 ARCHITECTURES: Dict[str, Tuple[Callable, Callable]] = {
     "Dozotar": (_dozotar_describe, _dozotar_tensor_names),
+    "Pidenex": (_pidenex_describe, _pidenex_tensor_names),
     "Nufusun": (_nufusun_describe, _nufusun_tensor_names),
     "Vanapel": (_vanapel_describe, _vanapel_tensor_names),
 }

@@ -55,19 +55,24 @@ class LayerDesc(C.Structure):
                 ("rope_original", C.c_int32), ("rope_base", C.c_float), ("rope_factor", C.c_float), ("rope_fast", C.c_float), ("rope_slow", C.c_float),
                 ("raw_input", C.c_int32), ("chunk", C.c_int32), ("conv_taps", C.c_int32), ("ssm_state", C.c_int32), ("ssm_groups", C.c_int32),
                 ("gate_norm_groups", C.c_int32), ("act_kind", C.c_int32), ("route_groups", C.c_int32), ("route_keep", C.c_int32),
-                ("route_renorm_eps", C.c_float), ("shared_ff", C.c_int32), ("shared_gate", C.c_int32)]
+                ("route_renorm_eps", C.c_float), ("shared_ff", C.c_int32), ("shared_gate", C.c_int32),
+                ("v_is_k", C.c_int32), ("pool", C.c_int32), ("lin_bias", C.c_int32), ("out_gate", C.c_int32), ("side_kind", C.c_int32),
+                ("side_width", C.c_int32), ("mix_scale", C.c_float), ("side_scale", C.c_float), ("rope_interleaved", C.c_int32),
+                ("mlp_ungated", C.c_int32), ("share_weights", C.c_int32), ("pass_embed", C.c_int32), ("pass_step", C.c_int32)]
 
 
 class ArchDesc(C.Structure):
     _fields_ = [("dim", C.c_int32), ("vocab_size", C.c_int32), ("n_layers", C.c_int32), ("n_ctx", C.c_int32), ("max_batch", C.c_int32),
                 ("norm_eps", C.c_float), ("embed_scale", C.c_float), ("norm_unit_offset", C.c_int32), ("compute", C.c_int32),
-                ("layers", C.POINTER(LayerDesc)), ("norm_groups", C.c_int32), ("norm_scalar", C.c_int32)]
+                ("layers", C.POINTER(LayerDesc)), ("norm_groups", C.c_int32), ("norm_scalar", C.c_int32), ("norm_kind", C.c_int32),
+                ("n_pass_steps", C.c_int32)]
 
 
 # the layer tensors after the expert lists, in the order of ps_cuda_arch_layer_weights
 ARCH_LAYER_VECTORS_2 = ("norm_mix_out", "norm_ff", "norm_ff_out", "r1", "r2", "sink", "vmix", "dq", "dq_norm", "uq", "dkv", "dkv_norm", "uk", "uv",
                         "q_norm", "k_norm", "q_conv", "k_conv", "v_conv", "g", "decay", "w_in", "conv_w", "conv_b", "dt_bias", "a_log", "d_skip", "mix_norm",
-                        "shared_gate", "shared_up", "shared_down", "shared_sg")
+                        "shared_gate", "shared_up", "shared_down", "shared_sg", "lin", "act", "side_z", "side_z_bias", "side_x", "side_x_bias", "side_g",
+                        "side_o")
 
 
 class ArchLayerWeights(C.Structure):
@@ -77,7 +82,7 @@ class ArchLayerWeights(C.Structure):
 
 
 class ArchWeights(C.Structure):
-    _fields_ = [("embed", Tensor), ("final_norm", Tensor), ("head", Tensor), ("layers", C.POINTER(ArchLayerWeights))]
+    _fields_ = [("embed", Tensor), ("final_norm", Tensor), ("head", Tensor), ("layers", C.POINTER(ArchLayerWeights)), ("pass_steps", Tensor)]
 
 
 COMPUTE_BF16, COMPUTE_F32 = 0, 1
@@ -88,7 +93,9 @@ SINK_NONE, SINK_ZERO, SINK_LEARNED = 0, 1, 2
 VMIX_NONE, VMIX_SOURCE, VMIX_BLEND = 0, 1, 2
 MIXER_RETENTION, MIXER_MAMBA2 = 3, 4
 QKNORM_NONE, QKNORM_HEAD, QKNORM_WHOLE = 0, 1, 2
-ACT_SWISH, ACT_GELU_TANH = 0, 1
+ACT_SWISH, ACT_GELU_TANH, ACT_XIELU = 0, 1, 2
+MIXER_MINGRU = 5
+NORM_RMS, NORM_LAYER = 0, 1
 ROUTER_SIGMOID, ROUTER_SOFTMAX = 1, 2
 
 _lib: Optional[C.CDLL] = None

@@ -53,9 +53,20 @@ struct PsArchLayer {
     float *q_norm = nullptr, *k_norm = nullptr, *decay = nullptr, *dt_bias = nullptr, *a_log = nullptr, *d_skip = nullptr, *mix_norm = nullptr;
     bf16 *wsg = nullptr, *wsu = nullptr, *wsd = nullptr; // shared expert
     uint8_t *t_sg = nullptr, *t_su = nullptr, *t_sd = nullptr;
+    // values from keys, output gate, side mixer: the first projection's rows are q | k | [v] | [gate] | [z | u | side gate]; the output
+    // projection reads [heads' outputs | side mixer's output] against [W_o | W_side_o] (od = its input width)
+    int v_off = 0, g_off = -1, z_off = 0; // where the value rows, the gate rows and the side mixer's rows start in a projected row
+    int ho = 0;                           // H * v_dim: the heads' outputs
+    float *lin = nullptr, *side_b = nullptr; // distance-bias slopes [H]; side mixer's biases z | u [2 W]
+    float act_a = 0.f, act_b = 0.f;       // xIELU: softplus(p), 1/2 + softplus(q)
+    int n_pool = 0;                       // pooled blocks of a cache set, padded to a multiple of 4
+    int64_t state_off = 0;                // the side mixer's state in the K buffer (floats from its start)
 };
 
 static inline PaAct pa_act_of(const ps_cuda_layer_desc &l) { return PaAct{l.act_limit, l.act_alpha, l.up_shift, l.act_kind}; }
+static inline PaAct pa_act_of(const PsArchLayer &w) {
+    return w.d.act_kind == PS_ACT_XIELU ? PaAct{0.f, w.act_a, w.act_b, PS_ACT_XIELU} : pa_act_of(w.d);
+}
 static inline PaRoute pa_route_of(const ps_cuda_layer_desc &l) {
     return PaRoute{l.n_experts, l.top_k, l.router_act, l.route_groups, l.route_keep, l.route_renorm, l.route_renorm_eps, l.shared_ff > 0 && l.shared_gate};
 }
@@ -77,8 +88,11 @@ struct PsArch {
     float *cq = nullptr, *lq = nullptr, *qa = nullptr, *att2 = nullptr; // latent attention: normed query latent, queries, queries with W_uk folded in, values after W_uv
     float *vsrc = nullptr; // value rows of the tokens in flight from the layer others blend theirs with
     float *x2 = nullptr;   // second residual buffer of the single-token step of sequential blocks
+    float *xe = nullptr;   // the embedding output, kept for the passes of a looped model that add it back
+    float *pass_steps = nullptr; // [n_pass_steps][dim]
+    int pool_off = 0, stat_off = 0; // where a score row keeps its pooled scores; where the single-token step keeps their block statistics
     float *cv = nullptr, *sh = nullptr, *ffo = nullptr, *sgate = nullptr; // convolution output; shared expert's output; summed feed-forward output; shared gate per token
-    int max_cv = 0;
+    int max_cv = 0, max_pool = 0;
     bool has_state = false; // some layer carries state that cannot be cut back (recurrences, convolution tails)
     int max_rq = 0, max_lq = 0, max_qa = 0, max_att2 = 0, vsrc_w = 0;
     int ldP = 0;
@@ -100,6 +114,7 @@ struct PsArch {
     int opt_pdl = 1;    // single-token kernels on the main stream are launched with programmatic stream serialisation
     int opt_scan_nc = 0; // value columns per lane of the recurrence scan (0: chosen by the grid's size)
     bool has_seq = false, has_par = false; // some layer is a sequential / a parallel block
+    bool keep_embed = false;               // some run adds the embedding output back
 };
 
 namespace {
@@ -274,18 +289,35 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
         PsArchLayer &w = a->L[(size_t)i];
         w.d = l;
         (l.block_kind == PS_BLOCK_SEQUENTIAL ? a->has_seq : a->has_par) = true;
+        if (l.pass_embed) a->keep_embed = true;
+        if ((l.pass_embed || l.pass_step) && l.block_kind != PS_BLOCK_SEQUENTIAL) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: passes open at sequential blocks", i));
+        if (l.share_weights < 0 || l.share_weights > i || l.pass_embed < 0 || l.pass_step < 0 || l.pass_step > d.n_pass_steps)
+            return bail(afail(err, PS_CUDA_ERR_INVALID, "layer %d: shares the weights of run %d, pass step %d of %d", i, l.share_weights - 1, l.pass_step, d.n_pass_steps));
+        if (l.share_weights > 0 && memcmp(&d.layers[l.share_weights - 1], &l, offsetof(ps_cuda_layer_desc, share_weights)) != 0)
+            return bail(afail(err, PS_CUDA_ERR_INVALID, "layer %d: a run that shares weights must have the sizes of run %d", i, l.share_weights - 1));
         if (l.mixer_kind < PS_MIXER_ATTENTION || l.mixer_kind > PS_MIXER_MAMBA2) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: unknown mixer kind %d", i, l.mixer_kind));
         const bool latent = l.mixer_kind == PS_MIXER_LATENT, recur = pa_recurrent(l);
-        w.gen2 = l.block_kind == PS_BLOCK_SEQUENTIAL && (l.raw_input || recur || l.conv_taps > 0 || l.qk_norm == PS_QKNORM_WHOLE || l.chunk > 0 || l.mlp_kind == PS_MLP_ROUTED ||
-                                                         l.rel_buckets > 0 || l.act_kind != PS_ACT_SWISH || l.shared_ff > 0);
-        if (!w.gen2 && (l.raw_input || recur || l.conv_taps > 0 || l.qk_norm == PS_QKNORM_WHOLE || l.chunk > 0 || l.act_kind != PS_ACT_SWISH || l.shared_ff > 0 ||
+        const bool newer = l.v_is_k || l.pool > 0 || l.lin_bias || l.out_gate || l.side_kind; // mechanisms of the general sequential layer only
+        w.gen2 = l.block_kind == PS_BLOCK_SEQUENTIAL && !latent &&
+                 (l.raw_input || recur || l.conv_taps > 0 || l.qk_norm == PS_QKNORM_WHOLE || l.chunk > 0 || l.mlp_kind == PS_MLP_ROUTED || l.rel_buckets > 0 ||
+                  l.act_kind == PS_ACT_GELU_TANH || l.shared_ff > 0 || newer);
+        if (newer && (!w.gen2 || l.mixer_kind != PS_MIXER_ATTENTION))
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: values from keys, pooled windows, linear distance biases, output gates and side mixers need an attention in a sequential block", i));
+        if (l.v_is_k && l.v_dim != l.qk_dim) return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: values from keys of size %d cannot have size %d", i, l.qk_dim, l.v_dim));
+        if (l.pool < 0 || (l.pool > 0 && (l.window <= 0 || l.chunk > 0 || l.conv_taps > 0 || l.rel_buckets > 0 || l.log_bias || l.lin_bias || l.head_mix)))
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: pooled blocks of %d need a window and go with no distance term, chunk, convolution or head mixing", i, l.pool));
+        if ((l.side_kind != 0 && (l.side_kind != PS_MIXER_MINGRU || l.side_width <= 0 || l.conv_taps > 0)) || (l.rope_interleaved && !latent))
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: side mixer %d of %d channels; interleaved rotation %d", i, l.side_kind, l.side_width, l.rope_interleaved));
+        if ((l.mlp_ungated && l.mlp_kind != PS_MLP_DENSE) || (l.act_kind == PS_ACT_XIELU && !l.mlp_ungated) || (d.norm_kind == PS_NORM_LAYER && (l.block_kind != PS_BLOCK_SEQUENTIAL || l.mlp_kind == PS_MLP_ROUTED)))
+            return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: a feed-forward without a gate is dense (xIELU has no gated form); layer norms go with sequential blocks and dense feed-forwards", i));
+        if (!w.gen2 && (l.raw_input || recur || l.conv_taps > 0 || l.qk_norm == PS_QKNORM_WHOLE || l.chunk > 0 || l.act_kind == PS_ACT_GELU_TANH || l.shared_ff > 0 ||
                         l.router_act == PS_ROUTER_SOFTMAX || l.route_groups > 1))
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: raw sublayer inputs, recurrent mixers, convolutions, whole-projection norms, chunked masks, gelu, soft-max / grouped routers and shared experts need a sequential block", i));
         if (w.gen2 && (latent || l.v_mix || l.qk_norm == PS_QKNORM_HEAD || l.proj_bias || l.head_mix || l.head_temp))
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: latent attention, value blending, per-head unit norms, projection biases and head mixing are not combined with this layer's other mechanisms", i));
         if (w.gen2 && l.mlp_kind == PS_MLP_ROUTED && !l.raw_input && d.norm_groups > 1)
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: routed experts behind a group norm", i));
-        if (l.chunk < 0 || l.conv_taps < 0 || l.conv_taps > 64 || l.act_kind < PS_ACT_SWISH || l.act_kind > PS_ACT_GELU_TANH || l.shared_ff < 0)
+        if (l.chunk < 0 || l.conv_taps < 0 || l.conv_taps > 64 || l.act_kind < PS_ACT_SWISH || l.act_kind > PS_ACT_XIELU || l.shared_ff < 0)
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: chunk %d, %d convolution taps, activation %d, shared expert of %d rows", i, l.chunk, l.conv_taps, l.act_kind, l.shared_ff));
         if (l.mixer_kind == PS_MIXER_RETENTION && (l.rope_dims < 0 || l.rope_dims > l.qk_dim || (l.rope_dims & 1) || (l.rope_dims > 0 && !(l.rope_base > 0.f)) || l.qk_dim > 256 || l.rope_factor != 0.f))
             return bail(afail(err, PS_CUDA_ERR_UNSUPPORTED, "layer %d: retention with heads of %d of which %d rotate (at most 256)", i, l.qk_dim, l.rope_dims));
@@ -322,6 +354,23 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
         w.qd = l.n_heads * a_dq; w.kd = l.n_kv_heads * a_dq; w.vd = l.n_kv_heads * a_dv; w.od = l.n_heads * l.v_dim;
         w.pw = latent ? l.q_rank + l.kv_rank + l.rot_dim : w.qd + w.kd + w.vd;
         w.aw = l.n_heads * a_dv;
+        w.ho = w.od;
+        w.v_off = w.qd + w.kd;
+        if (newer) { // q | k | [v] | [gate] | [z | u | side gate]
+            w.v_off = l.v_is_k ? w.qd : w.qd + w.kd;
+            w.pw = w.qd + w.kd + (l.v_is_k ? 0 : w.vd);
+            if (l.out_gate) { w.g_off = w.pw; w.pw += w.ho; }
+            if (l.side_kind) { w.z_off = w.pw; w.pw += 3 * l.side_width; w.od += l.side_width; w.aw = w.od; }
+            int64_t kf = (int64_t)w.kd * d.n_ctx, vf = (int64_t)w.vd * d.n_ctx;
+            if (l.pool > 0) {
+                w.n_pool = (d.n_ctx / l.pool + 3) & ~3;
+                kf += (int64_t)w.n_pool * w.kd;
+                vf += (int64_t)w.n_pool * w.vd;
+                a->max_pool = std::max(a->max_pool, w.n_pool);
+            }
+            if (l.side_kind) { w.state_off = kf; kf += l.side_width; }
+            w.k_floats = kf; w.v_floats = vf;
+        }
         if (l.mixer_kind == PS_MIXER_RETENTION) { // q | k | v | gate; the state S [H][v_dim][qk_dim padded] takes the place of the K rows
             w.qd = w.kd = l.n_heads * l.qk_dim; w.vd = w.od = w.aw = l.n_heads * l.v_dim;
             w.pw = 2 * w.qd + 2 * w.od;
@@ -336,7 +385,7 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
             w.conv_c = w.pw;
             w.k_floats = (int64_t)w.kd * d.n_ctx + (int64_t)(l.conv_taps - 1) * w.pw;
         }
-        if (recur || l.conv_taps > 1) a->has_state = true;
+        if (recur || l.conv_taps > 1 || l.side_kind) a->has_state = true;
         a->max_cv = std::max(a->max_cv, w.conv_c);
         if (l.shared_ff > 0) { a->max_ff = std::max(a->max_ff, l.shared_ff); a->max_k = std::max(a->max_k, l.shared_ff); }
         if (latent) {
@@ -369,7 +418,9 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
     }
     a->d.layers = nullptr; // the caller's array need not outlive this call: the copies live in L
     const int64_t B = d.max_batch, dim = d.dim;
-    a->ldS = ((int64_t)d.n_ctx + 3) & ~(int64_t)3;
+    if (d.norm_kind != PS_NORM_RMS && d.norm_kind != PS_NORM_LAYER) return bail(afail(err, PS_CUDA_ERR_INVALID, "unknown norm kind %d", d.norm_kind));
+    a->pool_off = (d.n_ctx + 3) & ~3;
+    a->ldS = (int64_t)a->pool_off + a->max_pool; // a score row: the tokens, then the pooled blocks
     int rc = 0;
     auto AL = [&](auto &ptr, size_t bytes) { if (!rc) rc = aalloc(a, (void **)&ptr, bytes, err); };
     AL(a->x, 4 * dim * B);
@@ -398,7 +449,9 @@ int ps_arch_create(PsArch **out, const ps_cuda_arch_desc *desc, std::string &err
     AL(a->sh, 4 * dim * B);
     AL(a->ffo, 4 * dim * B);
     AL(a->sgate, 4 * B);
-    a->ldP = (d.n_ctx + PA_DS_KEYS - 1) / PA_DS_KEYS;
+    a->stat_off = (d.n_ctx + PA_DS_KEYS - 1) / PA_DS_KEYS;
+    a->ldP = a->stat_off + (a->max_pool + PA_DS_KEYS - 1) / PA_DS_KEYS;
+    AL(a->xe, 4 * dim * B);
     AL(a->pm, 4 * (size_t)a->max_h * a->ldP);
     AL(a->pl, 4 * (size_t)a->max_h * a->ldP);
     AL(a->x2, 4 * dim);
@@ -507,10 +560,12 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
         int r = aalloc(a, (void **)dst, 2 * n, err);
         return r ? r : upload_mat(*dst, t, n, what, err);
     };
+    if (d.n_pass_steps > 0 && (rc = vec(&a->pass_steps, wt->pass_steps, (size_t)d.n_pass_steps * dim, "pass steps", false))) return rc;
     a->taps.assign((size_t)d.n_layers, nullptr);
     for (int i = 0; i < d.n_layers; i++) {
         PsArchLayer &w = a->L[(size_t)i];
         const ps_cuda_layer_desc &l = w.d;
+        if (l.share_weights > 0) continue; // a repeated run: it takes the pointers of its first run below
         const ps_cuda_arch_layer_weights &s = wt->layers[i];
         char nm[64];
         snprintf(nm, sizeof nm, "layer %d", i);
@@ -546,8 +601,22 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
                 return rc;
         } else {
             if ((rc = upload_mat(w.wqkv, s.q, nq * dim, "q", err)) || (rc = upload_mat(w.wqkv + nq * dim, s.k, nk * dim, "k", err)) ||
-                (rc = upload_mat(w.wqkv + (nq + nk) * dim, s.v, nv * dim, "v", err)))
+                (!l.v_is_k && (rc = upload_mat(w.wqkv + (nq + nk) * dim, s.v, nv * dim, "v", err))))
                 return rc;
+            if (l.out_gate && (rc = upload_mat(w.wqkv + (size_t)w.g_off * dim, s.g, (size_t)w.ho * dim, "output gate", err))) return rc;
+            if (l.lin_bias && (rc = vec(&w.lin, s.lin, (size_t)l.n_heads, "distance-bias slopes", false))) return rc;
+            if (l.side_kind) {
+                const size_t W = (size_t)l.side_width;
+                if ((rc = upload_mat(w.wqkv + (size_t)w.z_off * dim, s.side_z, W * dim, "side z", err)) || (rc = upload_mat(w.wqkv + ((size_t)w.z_off + W) * dim, s.side_x, W * dim, "side x", err)) ||
+                    (rc = upload_mat(w.wqkv + ((size_t)w.z_off + 2 * W) * dim, s.side_g, W * dim, "side gate", err)))
+                    return rc;
+                std::vector<float> b, part;
+                for (const ps_cuda_tensor *t : {&s.side_z_bias, &s.side_x_bias}) {
+                    if ((rc = small_to_f32(*t, W, part, "side mixer bias", err))) return rc;
+                    b.insert(b.end(), part.begin(), part.end());
+                }
+                if ((rc = upload_f32(a, &w.side_b, b, err))) return rc;
+            }
             if (l.mixer_kind == PS_MIXER_RETENTION) {
                 if ((rc = upload_mat(w.wqkv + (nq + nk + nv) * dim, s.g, nv * dim, "g", err)) || (rc = vec(&w.decay, s.decay, (size_t)l.n_heads, "decay", false))) return rc;
                 if (l.rope_dims > 0) {
@@ -567,7 +636,19 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
                 if ((rc = upload_f32(a, &w.conv_w, cw, err))) return rc;
             }
         }
-        if ((rc = aalloc(a, (void **)&w.wo, 2 * dim * (size_t)w.od, err)) || (rc = upload_mat(w.wo, s.o, dim * (size_t)w.od, "o", err))) return rc;
+        if ((rc = aalloc(a, (void **)&w.wo, 2 * dim * (size_t)w.od, err))) return rc;
+        if (l.side_kind) { // [W_o | W_side_o]: every output row reads the heads' outputs, then the side mixer's
+            const size_t ho = (size_t)w.ho, W = (size_t)l.side_width;
+            if (!s.o.host || !s.side_o.host || s.o.type != PS_TYPE_BF16 || s.side_o.type != PS_TYPE_BF16) return afail(err, PS_CUDA_ERR_INVALID, "bind: matrix o or side o is missing or not bfloat16");
+            std::vector<uint16_t> cat(dim * (ho + W));
+            for (size_t r = 0; r < dim; r++) {
+                memcpy(&cat[r * (ho + W)], static_cast<const uint16_t *>(s.o.host) + r * ho, 2 * ho);
+                memcpy(&cat[r * (ho + W) + ho], static_cast<const uint16_t *>(s.side_o.host) + r * W, 2 * W);
+            }
+            PA_CK(cudaMemcpy(w.wo, cat.data(), 2 * cat.size(), cudaMemcpyHostToDevice));
+        } else if ((rc = upload_mat(w.wo, s.o, dim * (size_t)w.od, "o", err))) {
+            return rc;
+        }
         if (l.block_kind == PS_BLOCK_SEQUENTIAL) {
             if (l.post_norm && (rc = normvec(&w.norm_mix_out, s.norm_mix_out, "norm of the mixer's output"))) return rc;
             if (l.mlp_kind != PS_MLP_NONE) {
@@ -617,8 +698,14 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
         }
         if (l.mlp_kind == PS_MLP_DENSE) {
             const size_t ff = (size_t)l.expert_ff;
-            if (!s.gate || !s.up || !s.down) return afail(err, PS_CUDA_ERR_INVALID, "bind: layer %d has no feed-forward tensors", i);
-            if ((rc = mat(&w.wgate, s.gate[0], ff * dim, "gate")) || (rc = mat(&w.wup, s.up[0], ff * dim, "up")) || (rc = mat(&w.wdown, s.down[0], ff * dim, "down"))) return rc;
+            if ((!l.mlp_ungated && !s.gate) || !s.up || !s.down) return afail(err, PS_CUDA_ERR_INVALID, "bind: layer %d has no feed-forward tensors", i);
+            if ((!l.mlp_ungated && (rc = mat(&w.wgate, s.gate[0], ff * dim, "gate"))) || (rc = mat(&w.wup, s.up[0], ff * dim, "up")) || (rc = mat(&w.wdown, s.down[0], ff * dim, "down"))) return rc;
+            if (l.act_kind == PS_ACT_XIELU) { // the two numbers of the activation become its two factors, formed once in double
+                if ((rc = small_to_f32(s.act, 2, tmp, "activation numbers", err))) return rc;
+                auto softplus = [](double v) { return std::log1p(std::exp(-std::fabs(v))) + std::max(v, 0.0); };
+                w.act_a = (float)softplus((double)tmp[0]);
+                w.act_b = (float)(0.5 + softplus((double)tmp[1]));
+            }
         }
     }
     if (a->round) {
@@ -634,10 +721,11 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
         if ((rc = tile(&a->t_head, a->head, 1, d.vocab_size, d.dim))) return rc;
         for (int i = 0; i < d.n_layers; i++) {
             PsArchLayer &w = a->L[(size_t)i];
+            if (w.d.share_weights > 0) continue;
             if ((rc = tile(&w.t_qkv, w.wqkv, 1, w.pw, d.dim)) || (rc = tile(&w.t_o, w.wo, 1, d.dim, w.od))) return rc;
             if (w.wuq && (rc = tile(&w.t_uq, w.wuq, 1, w.d.n_heads * (w.d.qk_dim + w.d.rot_dim), w.d.q_rank))) return rc;
             if (w.d.mlp_kind == PS_MLP_DENSE &&
-                ((rc = tile(&w.t_gate, w.wgate, 1, w.d.expert_ff, d.dim)) || (rc = tile(&w.t_up, w.wup, 1, w.d.expert_ff, d.dim)) || (rc = tile(&w.t_down, w.wdown, 1, d.dim, w.d.expert_ff))))
+                ((w.wgate && (rc = tile(&w.t_gate, w.wgate, 1, w.d.expert_ff, d.dim))) || (rc = tile(&w.t_up, w.wup, 1, w.d.expert_ff, d.dim)) || (rc = tile(&w.t_down, w.wdown, 1, d.dim, w.d.expert_ff))))
                 return rc;
             if (w.wsg && ((rc = tile(&w.t_sg, w.wsg, 1, w.d.shared_ff, d.dim)) || (rc = tile(&w.t_su, w.wsu, 1, w.d.shared_ff, d.dim)) || (rc = tile(&w.t_sd, w.wsd, 1, d.dim, w.d.shared_ff))))
                 return rc;
@@ -647,6 +735,13 @@ int ps_arch_bind(PsArch *a, const ps_cuda_arch_weights *wt, cudaStream_t stream,
                 return rc;
         }
         PA_CK(cudaStreamSynchronize(stream));
+    }
+    for (int i = 0; i < d.n_layers; i++) { // repeated runs: the first run's weights under the run's own description
+        PsArchLayer &w = a->L[(size_t)i];
+        if (w.d.share_weights <= 0) continue;
+        const ps_cuda_layer_desc keep = w.d;
+        w = a->L[(size_t)keep.share_weights - 1];
+        w.d = keep;
     }
     a->bound = true;
     return 0;
@@ -663,7 +758,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     auto cdiv = [](int64_t x, int64_t y) { return (unsigned)((x + y - 1) / y); };
     // single tokens take the single-token kernels; a model that mixes both block kinds, and taps of sequential blocks, take the batch kernels
     const bool single = bs == 1 && !a->opt_simple && !(a->has_seq && (a->has_par || a->taps_on));
-    const int groups = std::max(1, d.norm_groups);
+    const int groups = std::max(1, d.norm_groups), center = d.norm_kind == PS_NORM_LAYER;
     // warps sharing a row pair in the single-token mat-vecs: enough CTAs to fill the GPU when the matrix has few rows
     auto pick_ksplit = [&](int rows, int K) {
         int ks = 1;
@@ -680,12 +775,13 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     };
     const bool tc = ROUND && a->opt_tc && !single && !a->opt_simple;
     // C[m][n] = sum_k X[m][k] W[n][k] + bias[n] on the tensor cores: round + tile the activations, then the GEMM
-    auto tc_dense = [&](const float *X, int ldx, int M, int K, const uint8_t *wt, int N, const float *bias, float *C, int ldc) -> int {
+    auto tc_dense = [&](const float *X, int ldx, int M, int K, const uint8_t *wt, int N, const float *bias, float *C, int ldc, const PaAct *act1 = nullptr) -> int {
         const int nkb = (K + PT_KB - 1) / PT_KB, n_ct = (M + PT_N - 1) / PT_N, n_rt = (N + PT_M - 1) / PT_M;
         pa_k_tc_prep_x<<<dim3((unsigned)nkb, (unsigned)n_ct), 256, 0, st>>>(a->tcx, X, ldx, M, K, nkb, nullptr, nullptr, nullptr, nullptr, nullptr);
         PA_LAUNCH();
         PtArgs g{};
         g.a0 = wt; g.b = a->tcx; g.nkb = nkb; g.n_rt = n_rt; g.n_ct = n_ct; g.M = M; g.N = N; g.mode = PT_MODE_DENSE; g.C = C; g.ldc = ldc; g.bias = bias; g.err = io.err_dev;
+        if (act1) { g.act = *act1; g.act1 = 1; }
         pa_k_tc_gemm<1><<<std::min(a->n_sm, n_ct * n_rt), PT_THREADS, PT_SMEM, st>>>(g);
         PA_LAUNCH();
         return 0;
@@ -708,8 +804,10 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     auto attend = [&](const PaAttn &at, const float *q, int ldq, int kd, int li, int aw) -> int {
         int lo0 = at.window > 0 ? std::max(0, pos0 - at.window + 1) : 0; // the first key the first query sees
         if (at.chunk > 0) lo0 = std::max(lo0, pos0 - pos0 % at.chunk);
-        const int tile0 = lo0 / PA_TN;
-        pa_k_scores<<<dim3(cdiv(n_kv, PA_TN) - tile0, cdiv(bs, PA_TM), at.H), blk, 0, st>>>(at, q, ldq, io.kc[li], kd, a->S, io.pos_dev, bs, tile0);
+        const int tile0 = lo0 / PA_TN, tok_tiles = (int)cdiv(n_kv, PA_TN) - tile0;
+        // pooled blocks the batch's last query sees: further key tiles behind the token tiles
+        const int nv = (at.pool > 0 && n_kv - at.window >= at.pool) ? (n_kv - at.window) / at.pool : 0;
+        pa_k_scores<<<dim3(tok_tiles + cdiv(nv, PA_TN), cdiv(bs, PA_TM), at.H), blk, 0, st>>>(at, q, ldq, io.kc[li], kd, a->S, io.pos_dev, bs, tile0, tok_tiles);
         PA_LAUNCH();
         pa_k_mix_softmax<<<bs, 256, 4 * (size_t)at.H * at.H, st>>>(at, a->S, io.pos_dev, bs);
         PA_LAUNCH();
@@ -719,11 +817,13 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     };
     // sequential blocks: a sublayer's output waits here until the next seam adds it (normed) to the residual stream
     const float *pend_y = nullptr, *pend_w = nullptr;
+    // ... and what a new pass of a looped model adds before its first layer (the embedding output, a row of the pass steps)
+    const float *add_tok = nullptr, *add_vec = nullptr;
     auto seam = [&](float *h_out, const float *w_in) -> int {
-        if (!pend_y && !h_out) return 0;
-        pa_k_seam_norm<<<bs, 256, 0, st>>>(a->x, pend_y, pend_w, h_out, w_in, dim, groups, d.norm_eps);
+        if (!pend_y && !h_out && !add_tok && !add_vec) return 0;
+        pa_k_seam_norm<<<bs, 256, 0, st>>>(a->x, pend_y, pend_w, h_out, w_in, dim, groups, d.norm_eps, center, add_tok, add_vec);
         PA_LAUNCH();
-        pend_y = pend_w = nullptr;
+        pend_y = pend_w = add_tok = add_vec = nullptr;
         return 0;
     };
     // the single-token step of sequential blocks: the residual stream alternates between two buffers, because the CTA that stores the
@@ -731,8 +831,9 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     float *xc = a->x, *xo = a->x2;
     auto seam_mv = [&](PaMv &mv, const float *norm_w) {
         mv.x = xc; mv.groups = groups; mv.eps = d.norm_eps; mv.norm_w = norm_w; mv.seam_y = pend_y; mv.seam_w = pend_w;
-        if (pend_y) { mv.x_out = xo; std::swap(xc, xo); }
-        pend_y = pend_w = nullptr;
+        mv.center = center; mv.add_tok = add_tok; mv.add_vec = add_vec;
+        if (pend_y || add_tok || add_vec) { mv.x_out = xo; std::swap(xc, xo); }
+        pend_y = pend_w = add_tok = add_vec = nullptr;
     };
     auto dec_mv = [&](PaMv &mv, size_t smem) -> int {
         mv.ksplit = pick_ksplit(mv.N + mv.E, mv.K); mv.prefetch = a->opt_prefetch;
@@ -745,7 +846,8 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         unsigned blocks = cdiv(n_kv_cap, PA_DS_KEYS);
         if (at.window > 0) blocks = std::min(blocks, cdiv(at.window, PA_DS_KEYS) + 1);
         if (at.chunk > 0) blocks = std::min(blocks, cdiv(at.chunk, PA_DS_KEYS) + 1);
-        pa_launch_dep(pdl, pa_k_dec_scores, dim3(blocks), dim3(256), pa_dec_scores_smem(at.H, at.G, at.dq), st, at, q, (const float *)io.kc[li], io.pos_dev, a->S, io.err_dev);
+        const unsigned pooled = at.pool > 0 ? cdiv(n_kv_cap / at.pool, PA_DS_KEYS) : 0; // further CTAs for the pooled blocks
+        pa_launch_dep(pdl, pa_k_dec_scores, dim3(blocks + pooled), dim3(256), pa_dec_scores_smem(at.H, at.G, at.dq), st, at, q, (const float *)io.kc[li], io.pos_dev, a->S, io.err_dev, (int)blocks);
         PA_LAUNCH();
         pa_launch_dep(pdl, pa_k_dec_pv, dim3(cdiv(at.dv, PA_DP_DIMS), at.G, pa_dec_pv_split(at.H, at.G)), dim3(256), pa_dec_pv_smem(at.H, at.G), st, at, (const float *)a->S, (const float *)io.vct[li], io.pos_dev, a->att,
                       pa_dec_pv_chunk(at.H, at.G), io.err_dev);
@@ -790,6 +892,45 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         }
         return 0;
     };
+    // the dense feed-forward of a batch: gate | up (or up alone) with the activation in the product's epilogue, then down
+    auto dense_batch = [&](const float *X, const bf16 *wg, const bf16 *wu, const bf16 *wd, const uint8_t *tg, const uint8_t *tu, const uint8_t *td, int ff, const PaAct &act,
+                           float *out) -> int {
+        if (!wg) { // no gate
+            if (tc) {
+                int rc = tc_dense(X, dim, bs, dim, tu, ff, nullptr, a->y, ff, &act);
+                if (rc) return rc;
+            } else {
+                pa_k_dense_up1<ROUND><<<dim3(cdiv(ff, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(X, dim, wu, a->y, bs, ff, dim, act);
+                PA_LAUNCH();
+            }
+            return linear(a->y, ff, ff, wd, td, dim, out, dim);
+        }
+        if (tc) {
+            const int nkb = (dim + PT_KB - 1) / PT_KB, n_ct = (bs + PT_N - 1) / PT_N;
+            pa_k_tc_prep_x<<<dim3((unsigned)nkb, (unsigned)n_ct), 256, 0, st>>>(a->tcx, X, dim, bs, dim, nkb, nullptr, nullptr, nullptr, nullptr, nullptr);
+            PA_LAUNCH();
+            PtArgs g{};
+            g.a0 = tg; g.a1 = tu; g.b = a->tcx; g.nkb = nkb; g.n_rt = (ff + PT_M - 1) / PT_M; g.n_ct = n_ct; g.M = bs; g.N = ff; g.mode = PT_MODE_EXPERT_UP;
+            g.C = a->y; g.ldc = ff; g.act = act; g.err = io.err_dev;
+            pa_k_tc_gemm<2><<<std::min(a->n_sm, n_ct * g.n_rt), PT_THREADS, PT_SMEM, st>>>(g);
+        } else {
+            pa_k_dense_up<ROUND><<<dim3(cdiv(ff, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(X, dim, wg, wu, a->y, bs, ff, dim, act);
+        }
+        PA_LAUNCH();
+        return linear(a->y, ff, ff, wd, td, dim, out, dim);
+    };
+    // ... and of a single token: the seam in the prologue of the up rows' kernel, then the down rows; the output waits in `slot`
+    auto dense_single = [&](const PsArchLayer &w, const float *w_in) -> int {
+        const int ff = w.d.expert_ff;
+        const unsigned rows_cta = w.wgate ? PA_DV_ROWS / 2 : PA_DV_ROWS;
+        pa_launch_dep(pdl, pa_k_dec_dense_up<ROUND>, dim3(std::min(cdiv(ff, rows_cta), (unsigned)(4 * a->n_sm))), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, (const float *)xc, pend_y, pend_w, w_in,
+                      xo, groups, d.norm_eps, (const bf16 *)w.wgate, (const bf16 *)w.wup, a->y, ff, dim, pa_act_of(w), (const bf16 *)nullptr, 0, (float *)nullptr, center);
+        PA_LAUNCH();
+        std::swap(xc, xo);
+        PaMv mv{};
+        mv.x = a->y; mv.W = w.wdown; mv.N = dim; mv.K = ff; mv.y = a->slot;
+        return dec_mv(mv, 0);
+    };
     auto seq_layer = [&](int li) -> int {
         const PsArchLayer &w = a->L[(size_t)li];
         const ps_cuda_layer_desc &l = w.d;
@@ -812,7 +953,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         int ldq = w.pw;
         if (latent) {
             const int rq = l.q_rank, rk = l.kv_rank, dr = l.rot_dim, dn = l.qk_dim, lqw = H * (dn + dr);
-            const PaRope rope{w.rope_freq, l.rope_dims, w.rope_mscale};
+            const PaRope rope{w.rope_freq, l.rope_dims, w.rope_mscale, l.rope_interleaved};
             pa_k_latent_post<<<bs, 256, 0, st>>>(a->qkv, w.pw, rq, rk, dr, w.dq_norm, w.dkv_norm, d.norm_eps, rope, a->cq, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
             PA_LAUNCH();
             if (single) {
@@ -836,7 +977,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             if (l.qk_norm || l.v_mix)
                 pa_k_qkv_post<<<bs, 256, 0, st>>>(a->qkv, w.pw, H, G, l.qk_dim, l.v_dim, l.qk_norm, d.norm_eps, l.v_mix, w.vmix, a->vsrc, a->vsrc_w, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
             else
-                pa_k_kv_store<<<dim3(cdiv(w.kd + w.vd, 256), bs), 256, 0, st>>>(a->qkv, w.pw, w.qd, w.kd, w.vd, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
+                pa_k_kv_store<<<dim3(cdiv(w.kd + w.vd, 256), bs), 256, 0, st>>>(a->qkv, w.pw, w.qd, w.kd, w.vd, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev, w.qd + w.kd);
             PA_LAUNCH();
         }
         if (single) {
@@ -863,55 +1004,18 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             return rc;
         }
         pend_y = a->ao; pend_w = l.post_norm ? w.norm_mix_out : nullptr;
-        if (l.mlp_kind == PS_MLP_DENSE && single) {
-            const int ff = l.expert_ff;
-            float *xout = xo;
-            pa_launch_dep(pdl, pa_k_dec_dense_up<ROUND>, dim3(std::min(cdiv(ff, PA_DV_ROWS / 2), (unsigned)(4 * a->n_sm))), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, (const float *)xc,
-                          pend_y, pend_w, (const float *)w.norm_ff, xout, groups, d.norm_eps, (const bf16 *)w.wgate, (const bf16 *)w.wup, a->y, ff, dim, pa_act_of(l), (const bf16 *)nullptr, 0, (float *)nullptr);
-            PA_LAUNCH();
-            std::swap(xc, xo);
-            PaMv mv{};
-            mv.x = a->y; mv.W = w.wdown; mv.N = dim; mv.K = ff; mv.y = a->slot;
-            if ((rc = dec_mv(mv, 0))) return rc;
-            pend_y = a->slot; pend_w = l.post_norm ? w.norm_ff_out : nullptr;
-        } else if (l.mlp_kind == PS_MLP_DENSE) {
-            const int ff = l.expert_ff;
-            if ((rc = seam(a->h, w.norm_ff))) return rc;
-            if (tc) {
-                const int nkb = (dim + PT_KB - 1) / PT_KB, n_ct = (bs + PT_N - 1) / PT_N;
-                pa_k_tc_prep_x<<<dim3((unsigned)nkb, (unsigned)n_ct), 256, 0, st>>>(a->tcx, a->h, dim, bs, dim, nkb, nullptr, nullptr, nullptr, nullptr, nullptr);
-                PA_LAUNCH();
-                PtArgs g{};
-                g.a0 = w.t_gate; g.a1 = w.t_up; g.b = a->tcx; g.nkb = nkb; g.n_rt = (ff + PT_M - 1) / PT_M; g.n_ct = n_ct; g.M = bs; g.N = ff; g.mode = PT_MODE_EXPERT_UP;
-                g.C = a->y; g.ldc = ff; g.act = pa_act_of(l); g.err = io.err_dev;
-                pa_k_tc_gemm<2><<<std::min(a->n_sm, n_ct * g.n_rt), PT_THREADS, PT_SMEM, st>>>(g);
+        if (l.mlp_kind == PS_MLP_DENSE) {
+            if (single) {
+                if ((rc = dense_single(w, w.norm_ff))) return rc;
             } else {
-                pa_k_dense_up<ROUND><<<dim3(cdiv(ff, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(a->h, dim, w.wgate, w.wup, a->y, bs, ff, dim, pa_act_of(l));
+                if ((rc = seam(a->h, w.norm_ff))) return rc;
+                if ((rc = dense_batch(a->h, w.wgate, w.wup, w.wdown, w.t_gate, w.t_up, w.t_down, l.expert_ff, pa_act_of(w), a->slot))) return rc;
             }
-            PA_LAUNCH();
-            if ((rc = linear(a->y, ff, ff, w.wdown, w.t_down, dim, a->slot, dim))) return rc;
             pend_y = a->slot; pend_w = l.post_norm ? w.norm_ff_out : nullptr;
         }
         return 0;
     };
 
-    // the gated feed-forward of a batch: gate | up with the activation in the product's epilogue, then down
-    auto dense_batch = [&](const float *X, const bf16 *wg, const bf16 *wu, const bf16 *wd, const uint8_t *tg, const uint8_t *tu, const uint8_t *td, int ff, const PaAct &act,
-                           float *out) -> int {
-        if (tc) {
-            const int nkb = (dim + PT_KB - 1) / PT_KB, n_ct = (bs + PT_N - 1) / PT_N;
-            pa_k_tc_prep_x<<<dim3((unsigned)nkb, (unsigned)n_ct), 256, 0, st>>>(a->tcx, X, dim, bs, dim, nkb, nullptr, nullptr, nullptr, nullptr, nullptr);
-            PA_LAUNCH();
-            PtArgs g{};
-            g.a0 = tg; g.a1 = tu; g.b = a->tcx; g.nkb = nkb; g.n_rt = (ff + PT_M - 1) / PT_M; g.n_ct = n_ct; g.M = bs; g.N = ff; g.mode = PT_MODE_EXPERT_UP;
-            g.C = a->y; g.ldc = ff; g.act = act; g.err = io.err_dev;
-            pa_k_tc_gemm<2><<<std::min(a->n_sm, n_ct * g.n_rt), PT_THREADS, PT_SMEM, st>>>(g);
-        } else {
-            pa_k_dense_up<ROUND><<<dim3(cdiv(ff, PA_TN), cdiv(bs, PA_TM)), blk, 0, st>>>(X, dim, wg, wu, a->y, bs, ff, dim, act);
-        }
-        PA_LAUNCH();
-        return linear(a->y, ff, ff, wd, td, dim, out, dim);
-    };
     auto scan = [&](const PaScan &sc) -> int {
         // columns per lane: two when the grid still gives every SM a CTA (each k / q value read from shared memory then serves two columns)
         const int il = pa_scan_il(sc.dk);
@@ -972,20 +1076,32 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
                 q = a->cv;
             }
             if (l.qk_norm == PS_QKNORM_WHOLE)
-                pa_k_qkv_whole_norm<<<bs, 256, 0, st>>>(q, w.pw, w.qd, w.kd, w.vd, w.q_norm, w.k_norm, d.norm_eps, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
+                pa_k_qkv_whole_norm<<<bs, 256, 0, st>>>(q, w.pw, w.qd, w.kd, w.vd, w.q_norm, w.k_norm, d.norm_eps, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev, w.v_off);
             else
-                pa_k_kv_store<<<dim3(cdiv(w.kd + w.vd, 256), bs), 256, 0, st>>>(q, w.pw, w.qd, w.kd, w.vd, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
+                pa_k_kv_store<<<dim3(cdiv(w.kd + w.vd, 256), bs), 256, 0, st>>>(q, w.pw, w.qd, w.kd, w.vd, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev, w.v_off);
             PA_LAUNCH();
+            if (l.pool > 0) { // the means of the blocks that this batch completes (at most bs / pool + 1 of them)
+                pa_k_pool_blocks<<<dim3(cdiv(w.kd + w.vd, 256), (unsigned)(bs / l.pool + 1)), 256, 0, st>>>(io.kc[li], io.vct[li], w.kd, w.vd, d.n_ctx, l.pool, w.n_pool, io.pos_dev, bs);
+                PA_LAUNCH();
+            }
             PaAttn at{};
             at.H = H; at.G = l.n_kv_heads; at.dq = l.qk_dim; at.dv = l.v_dim; at.scale = l.score_scale; at.rel = w.rel; at.bucket = w.bucket; at.n_bucket = d.n_ctx;
             at.sink = l.sink != PS_SINK_NONE; at.sink_v = w.sink_v; at.r1 = w.r1; at.r2 = w.r2; at.window = l.window; at.chunk = l.chunk;
             at.n_ctx = d.n_ctx; at.ldS = a->ldS; at.B = B; at.pm = a->pm; at.pl = a->pl; at.ldP = a->ldP;
+            at.lin = w.lin; at.pool = l.pool; at.n_pool = w.n_pool; at.pool_off = a->pool_off; at.stat_off = a->stat_off;
             if (single) rc = attend_single(at, q, li);
             else rc = attend(at, q, w.pw, w.kd, li, w.aw);
             if (rc) return rc;
+            if (l.out_gate || l.side_kind) { // the heads' outputs through their gate; the side mixer's recurrence fills the columns behind them
+                const unsigned gate_ctas = cdiv(w.ho, 128), side_ctas = l.side_kind ? cdiv(l.side_width, 128) : 0;
+                pa_k_gate_gru<<<dim3(gate_ctas + side_ctas, (unsigned)std::min(bs, 64)), 128, 0, st>>>(a->att, w.aw, a->qkv, w.pw, w.ho, l.out_gate ? w.g_off : -1, l.side_kind ? l.mix_scale : 1.0f,
+                                                                                                     (int)gate_ctas, l.side_kind ? l.side_width : 0, w.z_off, w.side_b, l.side_kind ? w.side_b + l.side_width : nullptr,
+                                                                                                     l.side_scale, io.kc[li] + w.state_off, io.pos_dev, bs);
+                PA_LAUNCH();
+            }
         } else if (l.mixer_kind == PS_MIXER_RETENTION) {
             const int dq = l.qk_dim, dv = l.v_dim;
-            const PaRope rope{w.rope_freq, l.rope_dims, 1.0f};
+            const PaRope rope{w.rope_freq, l.rope_dims, 1.0f, 0};
             pa_k_rope_heads<<<dim3(cdiv(2 * H * dq, 256), bs), 256, 0, st>>>(a->qkv, w.pw, 2 * H, dq, rope, H, 1.0f / sqrtf((float)dq), io.pos_dev); // q | k rotated, k scaled
             PA_LAUNCH();
             PaScan sc{};
@@ -1026,18 +1142,12 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         pend_y = a->ao; pend_w = l.post_norm ? w.norm_mix_out : nullptr;
         if (l.mlp_kind == PS_MLP_NONE) return 0;
         const float *w_in = raw ? nullptr : w.norm_ff;
-        const PaAct act = pa_act_of(l);
+        const PaAct act = pa_act_of(w);
         const unsigned up_cap = (unsigned)(4 * a->n_sm);
         if (l.mlp_kind == PS_MLP_DENSE) {
             const int ff = l.expert_ff;
             if (single) {
-                pa_launch_dep(pdl, pa_k_dec_dense_up<ROUND>, dim3(std::min(cdiv(ff, PA_DV_ROWS / 2), up_cap)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, (const float *)xc, pend_y, pend_w, w_in,
-                              xo, groups, d.norm_eps, (const bf16 *)w.wgate, (const bf16 *)w.wup, a->y, ff, dim, act, (const bf16 *)nullptr, 0, (float *)nullptr);
-                PA_LAUNCH();
-                std::swap(xc, xo);
-                PaMv mv{};
-                mv.x = a->y; mv.W = w.wdown; mv.N = dim; mv.K = ff; mv.y = a->slot;
-                if ((rc = dec_mv(mv, 0))) return rc;
+                if ((rc = dense_single(w, w_in))) return rc;
             } else {
                 if ((rc = seam(raw ? nullptr : a->h, w_in))) return rc;
                 if ((rc = dense_batch(raw ? a->x : a->h, w.wgate, w.wup, w.wdown, w.t_gate, w.t_up, w.t_down, ff, act, a->slot))) return rc;
@@ -1052,7 +1162,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             const int n_rt = E + (rt.shared_gate ? 1 : 0); // the router's rows (+ the shared gate's): logits from the unrounded input
             if (sff > 0) { // the shared expert's gate | up launch carries the seam and the router's rows
                 pa_launch_dep(pdl, pa_k_dec_dense_up<ROUND>, dim3(std::min(cdiv(sff + n_rt, PA_DV_ROWS / 2), up_cap)), dim3(PA_DV_THREADS), 4 * (size_t)dim, st, (const float *)xc, pend_y, pend_w, w_in,
-                              xo, groups, d.norm_eps, (const bf16 *)w.wsg, (const bf16 *)w.wsu, a->y, sff, dim, act, (const bf16 *)w.router, n_rt, a->z);
+                              xo, groups, d.norm_eps, (const bf16 *)w.wsg, (const bf16 *)w.wsu, a->y, sff, dim, act, (const bf16 *)w.router, n_rt, a->z, 0);
                 PA_LAUNCH();
                 std::swap(xc, xo);
                 pend_y = pend_w = nullptr;
@@ -1086,11 +1196,13 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         return 0;
     };
 
-    pa_k_embed<<<bs, 128, 0, st>>>(a->x, a->embed, io.tokens_dev, dim, d.embed_scale);
+    pa_k_embed<<<bs, 128, 0, st>>>(a->x, a->embed, io.tokens_dev, dim, d.embed_scale, a->keep_embed ? a->xe : nullptr);
     PA_LAUNCH();
     for (int li = 0; li < d.n_layers; li++) {
         const PsArchLayer &w = a->L[(size_t)li];
         const ps_cuda_layer_desc &l = w.d;
+        if (l.pass_embed) add_tok = a->xe;   // a new pass: the run's first seam adds these to the stream
+        if (l.pass_step) add_vec = a->pass_steps + (int64_t)(l.pass_step - 1) * dim;
         if (l.block_kind == PS_BLOCK_SEQUENTIAL) {
             int rc = w.gen2 ? gen_layer(li) : seq_layer(li);
             if (rc) return rc;
@@ -1135,7 +1247,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         }
         PA_LAUNCH();
         if (!single) {
-            pa_k_kv_store<<<dim3(cdiv(w.kd + w.vd, 256), bs), 256, 0, st>>>(a->qkv, nqkv, w.qd, w.kd, w.vd, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev);
+            pa_k_kv_store<<<dim3(cdiv(w.kd + w.vd, 256), bs), 256, 0, st>>>(a->qkv, nqkv, w.qd, w.kd, w.vd, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev, w.qd + w.kd);
             PA_LAUNCH();
         }
         PaAttn at{};
@@ -1143,12 +1255,12 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         at.H = H; at.G = G; at.dq = dq; at.dv = dv; at.scale = l.score_scale; at.temp = w.temp; at.rel = w.rel; at.bucket = w.bucket; at.n_bucket = d.n_ctx;
         at.mix = w.mix; at.sink = l.sink != PS_SINK_NONE; at.n_ctx = d.n_ctx; at.ldS = a->ldS; at.B = B; at.pm = a->pm; at.pl = a->pl; at.ldP = a->ldP;
         if (single) {
-            pa_launch_dep(pdl, pa_k_dec_scores, dim3(cdiv(n_kv_cap, PA_DS_KEYS)), dim3(256), pa_dec_scores_smem(H, G, dq), st, at, (const float *)a->qkv, (const float *)io.kc[li], io.pos_dev, a->S, io.err_dev);
+            pa_launch_dep(pdl, pa_k_dec_scores, dim3(cdiv(n_kv_cap, PA_DS_KEYS)), dim3(256), pa_dec_scores_smem(H, G, dq), st, at, (const float *)a->qkv, (const float *)io.kc[li], io.pos_dev, a->S, io.err_dev, (int)cdiv(n_kv_cap, PA_DS_KEYS));
             PA_LAUNCH();
             pa_launch_dep(pdl, pa_k_dec_pv, dim3(cdiv(dv, PA_DP_DIMS), G, pa_dec_pv_split(H, G)), dim3(256), pa_dec_pv_smem(H, G), st, at, (const float *)a->S, (const float *)io.vct[li], io.pos_dev, a->att, pa_dec_pv_chunk(H, G), io.err_dev);
             PA_LAUNCH();
         } else {
-            pa_k_scores<<<dim3(cdiv(n_kv, PA_TN), cdiv(bs, PA_TM), H), blk, 0, st>>>(at, a->qkv, nqkv, io.kc[li], w.kd, a->S, io.pos_dev, bs, 0);
+            pa_k_scores<<<dim3(cdiv(n_kv, PA_TN), cdiv(bs, PA_TM), H), blk, 0, st>>>(at, a->qkv, nqkv, io.kc[li], w.kd, a->S, io.pos_dev, bs, 0, (int)cdiv(n_kv, PA_TN));
             PA_LAUNCH();
             pa_k_mix_softmax<<<bs, 256, 4 * (size_t)H * H, st>>>(at, a->S, io.pos_dev, bs);
             PA_LAUNCH();
@@ -1198,7 +1310,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
     }
     if (lm_head) {
         if (!single) {
-            if (pend_y || groups > 1) {
+            if (pend_y || groups > 1 || center) {
                 int rc = seam(a->h, a->final_norm);
                 if (rc) return rc;
             } else {

@@ -89,32 +89,29 @@ __device__ __forceinline__ void pa_norm_to_smem(float *hs, const float *__restri
     __syncthreads();
 }
 
-// block-wide seam of a sequential block (256 threads): hs = G(x + P(y); w_in) with P(y) = G(y; w_out) (w_out null: y itself; y null:
-// nothing joins), G over `groups` equal parts.  CTA 0 also stores the updated residual to x_out - a buffer other than x, which the
-// other CTAs are still reading.
+// block-wide seam of a sequential block (256 threads): hs = G(x + P(y) + add_tok + add_vec; w_in) with P(y) = G(y; w_out) (w_out
+// null: y itself; y / add_tok / add_vec null: nothing joins), G over `groups` equal parts, the part's mean taken off first when
+// `center`.  CTA 0 also stores the updated residual to x_out - a buffer other than x, which the other CTAs are still reading.
 __device__ __forceinline__ void pa_seam_to_smem(float *hs, const float *__restrict__ x, const float *__restrict__ y, const float *__restrict__ w_out,
-                                                const float *__restrict__ w_in, float *__restrict__ x_out, int dim, int groups, float eps) {
+                                                const float *__restrict__ w_in, float *__restrict__ x_out, int dim, int groups, float eps, int center = 0,
+                                                const float *__restrict__ add_tok = nullptr, const float *__restrict__ add_vec = nullptr) {
     __shared__ float red[8];
     const int gs = dim / groups;
     for (int g = 0; g < groups; g++) {
         const int c0 = g * gs;
-        float inv = 1.0f;
-        if (y && w_out) {
-            float s = 0.f;
-            for (int c = threadIdx.x; c < gs; c += 256) s = fmaf(y[c0 + c], y[c0 + c], s);
-            inv = 1.0f / sqrtf(pa_block_sum(s, red) / (float)gs + eps);
-        }
-        float s2 = 0.f;
+        float inv = 1.0f, mu = 0.f;
+        if (y && w_out) inv = pa_block_stats(y + c0, gs, center, eps, red, mu);
         for (int c = threadIdx.x; c < gs; c += 256) {
             float v = x[c0 + c];
-            if (y) v += w_out ? y[c0 + c] * inv * w_out[c0 + c] : y[c0 + c];
+            if (y) v += w_out ? (y[c0 + c] - mu) * inv * w_out[c0 + c] : y[c0 + c];
+            if (add_tok || add_vec) v += (add_tok ? add_tok[c0 + c] : 0.f) + (add_vec ? add_vec[c0 + c] : 0.f);
             hs[c0 + c] = v;
             if (x_out && blockIdx.x == 0 && blockIdx.y == 0) x_out[c0 + c] = v;
-            s2 = fmaf(v, v, s2);
         }
         if (w_in) {
-            const float inv2 = 1.0f / sqrtf(pa_block_sum(s2, red) / (float)gs + eps);
-            for (int c = threadIdx.x; c < gs; c += 256) hs[c0 + c] = hs[c0 + c] * inv2 * w_in[c0 + c]; // (a thread's own entries)
+            float mu2;
+            const float inv2 = pa_block_stats(hs + c0, gs, center, eps, red, mu2); // (a thread's own entries)
+            for (int c = threadIdx.x; c < gs; c += 256) hs[c0 + c] = (hs[c0 + c] - mu2) * inv2 * w_in[c0 + c];
         }
     }
     __syncthreads();
@@ -128,6 +125,8 @@ struct PaMv {
     int groups;
     const float *seam_y, *seam_w;
     float *x_out;
+    int center;            // the norms take the mean off first
+    const float *add_tok, *add_vec; // what a new pass of a looped model adds to the stream at this seam (null: nothing)
     // per-head products (grp_rows > 0): rows [g * grp_rows, (g + 1) * grp_rows) read x + g * x_gs and write y + g * y_gs
     int grp_rows, x_gs, y_gs;
     const bf16 *W;         // [N][K]
@@ -169,7 +168,7 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_mv(const PaMv a) {
     ps_grid_dep_wait();
     const float *xin = a.x;
     if (a.groups > 0) {
-        pa_seam_to_smem(pa_hs, a.x, a.seam_y, a.seam_w, a.norm_w, a.x_out, a.K, a.groups, a.eps);
+        pa_seam_to_smem(pa_hs, a.x, a.seam_y, a.seam_w, a.norm_w, a.x_out, a.K, a.groups, a.eps, a.center, a.add_tok, a.add_vec);
         xin = pa_hs;
     } else if (a.norm_w) {
         pa_norm_to_smem(pa_hs, a.x, a.norm_w, a.K, a.eps);
@@ -232,8 +231,9 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_mv(const PaMv a) {
 // b[h][j] for the CTA's PA_DS_KEYS keys.  The keys' cache rows arrive in shared memory by 1-D bulk copies (one per row, the rows
 // padded against bank conflicts) while the threads fetch q; then a thread per (key, head) forms the dot product with float4 reads
 // and applies scale / temperature / distance bias - no shuffles, and the bias look-ups of all pairs are in flight together.
+// CTAs from `tok_blocks` on take 16 pooled blocks each: the mean key rows behind the token rows, scores at pool_off, statistics at stat_off.
 __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *__restrict__ q, const float *__restrict__ kc, const int32_t *__restrict__ pos_dev,
-                                                       float *__restrict__ b, int *__restrict__ err) {
+                                                       float *__restrict__ b, int *__restrict__ err, int tok_blocks) {
     extern __shared__ __align__(16) float sm[];
     __shared__ __align__(8) uint64_t bar;
     const int H = at.H, G = at.G, dq = at.dq, rep = H / G, kd = G * dq, kds = ((kd + 3) & ~3) + 4;
@@ -245,10 +245,20 @@ __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *_
     if (at.mix) for (int t = tid; t < H * H; t += 256) Ts[t] = at.mix[t]; // a weight: fetched before the dependency wait
     ps_grid_dep_launch();
     ps_grid_dep_wait();
-    const int pos = pos_dev[0], lo = pa_first_key(at, pos);
-    const int blk = lo / PA_DS_KEYS + blockIdx.x, j0 = blk * PA_DS_KEYS; // the grid starts at the block of the first key in sight
-    if (j0 > pos) return;
-    const int nj = min(PA_DS_KEYS, pos + 1 - j0);
+    const int pos = pos_dev[0];
+    const bool pooled = (int)blockIdx.x >= tok_blocks;
+    int lo = pa_first_key(at, pos);
+    int blk = lo / PA_DS_KEYS + blockIdx.x, j0 = blk * PA_DS_KEYS; // the grid starts at the block of the first key in sight
+    int nj = min(PA_DS_KEYS, pos + 1 - j0), s_off = 0;
+    if (pooled) { // rows n_ctx + j0 .. of the K buffer; every one of the first pa_pool_vis blocks is in sight
+        lo = 0;
+        j0 = ((int)blockIdx.x - tok_blocks) * PA_DS_KEYS;
+        nj = min(PA_DS_KEYS, pa_pool_vis(at, pos) - j0);
+        blk = at.stat_off + (int)blockIdx.x - tok_blocks;
+        s_off = at.pool_off;
+        kc += (int64_t)at.n_ctx * kd;
+    }
+    if (nj <= 0) return;
     const bool bulk = (kd & 3) == 0;
     if (bulk && tid == 0) {
         ps_mbar_init(&bar, 1);
@@ -277,7 +287,7 @@ __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *_
             s = 0.f;
             for (int d = 0; d < dq; d++) s = fmaf(kr[d], qr[d], s);
         }
-        sa[h * (PA_DS_KEYS + 1) + jj] = pa_score(at, s, h, pos - (j0 + jj));
+        sa[h * (PA_DS_KEYS + 1) + jj] = pa_score(at, s, h, pooled ? 0 : pos - (j0 + jj));
     }
     __syncthreads();
     // mix the heads, store, and leave the block's soft-max statistics (max, sum of exponentials) for the P.V kernel:
@@ -294,7 +304,7 @@ __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *_
             } else {
                 s = sa[h * (PA_DS_KEYS + 1) + jj];
             }
-            b[(int64_t)h * at.ldS + j0 + jj] = s;
+            b[(int64_t)h * at.ldS + s_off + j0 + jj] = s;
         }
         float m = s;
 #pragma unroll
@@ -339,15 +349,18 @@ __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__res
     }
     // soft-max statistics of every head of the group from the scores kernel's per-block pairs: a warp per head
     const int nb = (n + PA_DS_KEYS - 1) / PA_DS_KEYS;
+    const int nv = pa_pool_vis(at, n - 1), nvb = (nv + PA_DS_KEYS - 1) / PA_DS_KEYS; // pooled blocks in sight, and their statistics
     for (int r = warp; r < rep; r += 8) {
         const float *bm = at.pm + (int64_t)(h0 + r) * at.ldP, *bl = at.pl + (int64_t)(h0 + r) * at.ldP;
         const float sk = pa_sink_logit(at, h0 + r);
         float mx = at.sink ? sk : -INFINITY;
         for (int j = lo / PA_DS_KEYS + lane; j < nb; j += 32) mx = fmaxf(mx, bm[j]);
+        for (int j = lane; j < nvb; j += 32) mx = fmaxf(mx, bm[at.stat_off + j]);
 #pragma unroll
         for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         float sum = 0.f;
         for (int j = lo / PA_DS_KEYS + lane; j < nb; j += 32) sum = fmaf(bl[j], expf(bm[j] - mx), sum);
+        for (int j = lane; j < nvb; j += 32) sum = fmaf(bl[at.stat_off + j], expf(bm[at.stat_off + j] - mx), sum);
 #pragma unroll
         for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
         if (lane == 0) {
@@ -360,25 +373,29 @@ __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__res
     const int dim_l = warp % PA_DP_DIMS, part = warp / PA_DP_DIMS, n_part = 8 / PA_DP_DIMS;
     const int c0 = blockIdx.x * PA_DP_DIMS;
     int it = 0;
-    for (int j0 = lo & ~3; j0 < n; j0 += chunk, it++) { // (bulk copies start on 16-byte boundaries)
-        const int nj = min(chunk, n - j0), nj4 = (nj + 3) & ~3;
+    // two stretches of keys: the tokens in sight (V^T rows of n_ctx columns), then the pooled blocks (rows of n_pool columns behind them)
+    for (int seg = 0; seg < (nv > 0 ? 2 : 1); seg++) {
+    const float *vbase = seg ? vct + (int64_t)G * dv * at.n_ctx : vct;
+    const int ldv = seg ? at.n_pool : at.n_ctx, s_lo = seg ? 0 : lo, s_n = seg ? nv : n, s_off = seg ? at.pool_off : 0;
+    for (int j0 = s_lo & ~3; j0 < s_n; j0 += chunk, it++) { // (bulk copies start on 16-byte boundaries)
+        const int nj = min(chunk, s_n - j0), nj4 = (nj + 3) & ~3;
         __syncthreads(); // the previous chunk's buffers are free
         if (bulk) {
             if (tid == 0) {
                 const int rows = min(PA_DP_DIMS, dv - c0);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // the rows were read through the generic proxy
                 ps_mbar_expect_tx(&bar, (uint32_t)(rows * nj4 * 4));
-                for (int cc = 0; cc < rows; cc++) ps_bulk_g2s(vs + cc * chunk, vct + (int64_t)(g * dv + c0 + cc) * at.n_ctx + j0, (uint32_t)(nj4 * 4), &bar);
+                for (int cc = 0; cc < rows; cc++) ps_bulk_g2s(vs + cc * chunk, vbase + (int64_t)(g * dv + c0 + cc) * ldv + j0, (uint32_t)(nj4 * 4), &bar);
             }
         } else {
             for (int t = tid; t < PA_DP_DIMS * nj4; t += 256) {
                 const int cc = t / nj4, jj = t % nj4;
-                vs[cc * chunk + jj] = (c0 + cc < dv && jj < nj) ? vct[(int64_t)(g * dv + c0 + cc) * at.n_ctx + j0 + jj] : 0.f;
+                vs[cc * chunk + jj] = (c0 + cc < dv && jj < nj) ? vbase[(int64_t)(g * dv + c0 + cc) * ldv + j0 + jj] : 0.f;
             }
         }
         for (int t = tid; t < rep * nj4; t += 256) {
             const int r = t / nj4, jj = t % nj4;
-            ps[r * chunk + jj] = (jj < nj && j0 + jj >= lo) ? expf(b[(int64_t)(h0 + r) * at.ldS + j0 + jj] - ms[r]) : 0.f;
+            ps[r * chunk + jj] = (jj < nj && j0 + jj >= s_lo) ? expf(b[(int64_t)(h0 + r) * at.ldS + s_off + j0 + jj] - ms[r]) : 0.f;
         }
         __syncthreads();
         if (bulk && !ps_tc_wait(&bar, it & 1)) { if (tid == 0) err[0] = 6; return; }
@@ -396,6 +413,7 @@ __global__ void __launch_bounds__(256) pa_k_dec_pv(PaAttn at, const float *__res
                 if (lane == 0) acc[warp * rep + r] += s;
             }
         }
+    }
     }
     __syncthreads();
     for (int t = tid; t < PA_DP_DIMS * rep; t += 256) {
@@ -448,16 +466,31 @@ template <bool ROUND>
 __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_dense_up(const float *__restrict__ x, const float *__restrict__ seam_y, const float *__restrict__ seam_w,
                                                                    const float *__restrict__ norm_w, float *__restrict__ x_out, int groups, float eps, const bf16 *__restrict__ Wg,
                                                                    const bf16 *__restrict__ Wu, float *__restrict__ y, int ff, int dim, PaAct act,
-                                                                   const bf16 *__restrict__ Wr = nullptr, int E = 0, float *__restrict__ z = nullptr) {
+                                                                   const bf16 *__restrict__ Wr = nullptr, int E = 0, float *__restrict__ z = nullptr, int center = 0) {
     extern __shared__ __align__(16) float pa_hs[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, rows = PA_DV_ROWS / 2;
+    if (!Wg) { // no gate: a warp's pair is two neighbouring up rows, y[n] = act(up[n] . h)
+        const int n = (blockIdx.x * rows + warp) * 2;
+        if (n < ff) pa_prefetch2(Wu + (int64_t)n * dim, Wu + (int64_t)min(n + 1, ff - 1) * dim, 0, dim, lane);
+        ps_grid_dep_launch();
+        ps_grid_dep_wait();
+        pa_seam_to_smem(pa_hs, x, seam_y, seam_w, norm_w, x_out, dim, groups, eps, center);
+        for (int n0 = (blockIdx.x * rows + warp) * 2; n0 < ff; n0 += gridDim.x * rows * 2) {
+            const int n1 = min(n0 + 1, ff - 1);
+            float s0, s1;
+            pa_dot2<ROUND>(Wu + (int64_t)n0 * dim, Wu + (int64_t)n1 * dim, pa_hs, dim, 1.0f, lane, s0, s1);
+            if (lane == 0) y[n0] = pa_act1(s0, act);
+            if (lane == 1 && n1 != n0) y[n1] = pa_act1(s1, act);
+        }
+        return;
+    }
     {
         const int n = blockIdx.x * rows + warp;
         if (n < ff) pa_prefetch2(Wg + (int64_t)n * dim, Wu + (int64_t)n * dim, 0, dim, lane);
     }
     ps_grid_dep_launch();
     ps_grid_dep_wait();
-    pa_seam_to_smem(pa_hs, x, seam_y, seam_w, norm_w, x_out, dim, groups, eps);
+    pa_seam_to_smem(pa_hs, x, seam_y, seam_w, norm_w, x_out, dim, groups, eps, center);
     // E more rows behind the ff rows: a router's logits z[e] = Wr[e] . h from the UNROUNDED input (a shared expert's launch carries them)
     for (int n = blockIdx.x * rows + warp; n < ff + E; n += gridDim.x * rows) {
         float gsum, usum;

@@ -16,6 +16,8 @@
 
 // activation of a gated unit: PS_ACT_SWISH  g' sigmoid(alpha g') (u' + shift) on g' = min(g, limit), u' = clamp(u, +-limit)
 //                             PS_ACT_GELU_TANH  the tanh form of gelu on g, times u
+//                             PS_ACT_XIELU      one argument only: alpha z^2 + z / 2 above zero, shift (exp(z) - 1 - z) + z / 2 below
+//                                               (alpha = softplus(p), shift = 1/2 + softplus(q) of the layer's two numbers)
 struct PaAct {
     float limit, alpha, shift;
     int kind;
@@ -34,6 +36,11 @@ struct PaAttn {
     const float *r1, *r2;   // [H] each or null: score -= r1[h] * ln(1 + r2[h] * distance)
     int window;             // > 0: a query sees the keys at distances 0 .. window - 1 only
     int chunk;              // > 0: a query sees the keys of its own chunk of positions only (chunks counted from position 0)
+    const float *lin;       // [H] or null: score -= lin[h] * distance
+    // pool > 0 (with a window): one mean key / value per block of `pool` positions that lies wholly before the window.  The means sit
+    // behind the token rows of the cache buffers (K: row n_ctx + b; V^T: [G * dv][n_pool] behind the token part); a query's pooled
+    // scores sit at pool_off + b of its score row, the single-token step's block statistics from stat_off on
+    int pool, n_pool, pool_off, stat_off;
     int n_ctx;
     int64_t ldS;            // row stride of the score rows
     int B;                  // rows per head in the score buffer (max_batch)
@@ -93,23 +100,32 @@ __device__ __forceinline__ void pa_tile_mm(float (&acc)[NB][4][4], const float *
     __shared__ __align__(16) float Bs[NB][PA_TK][PA_LD]
 
 // ---------------------------------------------------------------------------------------------------------------- small ops
-__global__ void __launch_bounds__(128) pa_k_embed(float *__restrict__ x, const bf16 *__restrict__ table, const int32_t *__restrict__ tokens, int dim, float scale) {
+// keep (null or [tokens][dim]) receives the same rows once more: the embedding output that later passes of a looped model add back
+__global__ void __launch_bounds__(128) pa_k_embed(float *__restrict__ x, const bf16 *__restrict__ table, const int32_t *__restrict__ tokens, int dim, float scale,
+                                                  float *__restrict__ keep) {
     const int t = blockIdx.x;
     const bf16 *row = table + (int64_t)tokens[t] * dim;
     float *out = x + (int64_t)t * dim;
+    float *out2 = keep ? keep + (int64_t)t * dim : nullptr;
     if ((dim & 7) == 0) { // 16-byte loads: the whole row is in flight at once
         for (int c = threadIdx.x * 8; c < dim; c += blockDim.x * 8) {
             const uint4 v = __ldg(reinterpret_cast<const uint4 *>(row + c));
             const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                out[c + 2 * i] = __uint_as_float(u[i] << 16) * scale;
-                out[c + 2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u) * scale;
+                const float lo = __uint_as_float(u[i] << 16) * scale, hi = __uint_as_float(u[i] & 0xffff0000u) * scale;
+                out[c + 2 * i] = lo;
+                out[c + 2 * i + 1] = hi;
+                if (out2) { out2[c + 2 * i] = lo; out2[c + 2 * i + 1] = hi; }
             }
         }
         return;
     }
-    for (int c = threadIdx.x; c < dim; c += blockDim.x) out[c] = __bfloat162float(row[c]) * scale;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+        const float v = __bfloat162float(row[c]) * scale;
+        out[c] = v;
+        if (out2) out2[c] = v;
+    }
 }
 
 // h = x / sqrt(mean(x^2) + eps) * w   (w already holds 1 + weight for unit-offset norms)
@@ -134,13 +150,33 @@ __global__ void __launch_bounds__(256) pa_k_norm(float *__restrict__ h, const fl
 }
 
 // the batch's K rows go to kc[pos][:], its V rows transposed to vct[:][pos]
+// (v_off: where the value rows start in a projected row - behind the keys, or AT the keys when the values are the keys)
 __global__ void __launch_bounds__(256) pa_k_kv_store(const float *__restrict__ qkv, int ld, int qd, int kd, int vd, float *__restrict__ kc, float *__restrict__ vct, int n_ctx,
-                                                     const int32_t *__restrict__ pos) {
+                                                     const int32_t *__restrict__ pos, int v_off) {
     const int t = blockIdx.y, c = blockIdx.x * 256 + threadIdx.x;
     const int p = pos[t];
-    const float *row = qkv + (int64_t)t * ld + qd;
-    if (c < kd) kc[(int64_t)p * kd + c] = row[c];
-    else if (c < kd + vd) vct[(int64_t)(c - kd) * n_ctx + p] = row[c];
+    const float *row = qkv + (int64_t)t * ld;
+    if (c < kd) kc[(int64_t)p * kd + c] = row[qd + c];
+    else if (c < kd + vd) vct[(int64_t)(c - kd) * n_ctx + p] = row[v_off + c - kd];
+}
+
+// The means of the blocks of `pool` positions that the batch completes (block b ends at position b pool + pool - 1): K row n_ctx + b
+// and column b of the pooled V^T rows, each the sum of the block's cached entries in position order times 1 / pool - so a mean does
+// not depend on how the prompt was cut.  Grid (channels / 256, candidate blocks); the batch's first position comes from device memory.
+__global__ void __launch_bounds__(256) pa_k_pool_blocks(float *__restrict__ kc, float *__restrict__ vct, int kd, int vd, int n_ctx, int pool, int n_pool,
+                                                        const int32_t *__restrict__ pos, int bs) {
+    const int p0 = pos[0], b = p0 / pool + blockIdx.y, c = blockIdx.x * 256 + threadIdx.x;
+    if ((int64_t)(b + 1) * pool > p0 + bs || (int64_t)(b + 1) * pool > n_ctx || c >= kd + vd) return;
+    const int j0 = b * pool;
+    float s = 0.f;
+    if (c < kd) {
+        for (int j = 0; j < pool; j++) s += kc[(int64_t)(j0 + j) * kd + c];
+        kc[(int64_t)(n_ctx + b) * kd + c] = s / (float)pool;
+    } else {
+        const float *vr = vct + (int64_t)(c - kd) * n_ctx + j0;
+        for (int j = 0; j < pool; j++) s += vr[j];
+        vct[(int64_t)vd * n_ctx + (int64_t)(c - kd) * n_pool + b] = s / (float)pool;
+    }
 }
 
 // x += mixer + sum of the feed-forward slots (fixed order)
@@ -165,31 +201,45 @@ __device__ __forceinline__ float pa_block_sum(float s, float *red) {
     return t;
 }
 
+// block-wide statistics of v[0 .. n) (each thread its own strided entries): mu = mean when `center`, else 0;
+// returns 1 / sqrt(mean((v - mu)^2) + eps)
+__device__ __forceinline__ float pa_block_stats(const float *v, int n, int center, float eps, float *red, float &mu) {
+    mu = 0.f;
+    if (center) {
+        float m = 0.f;
+        for (int c = threadIdx.x; c < n; c += 256) m += v[c];
+        mu = pa_block_sum(m, red) / (float)n;
+    }
+    float s = 0.f;
+    for (int c = threadIdx.x; c < n; c += 256) { const float d = v[c] - mu; s = fmaf(d, d, s); }
+    return 1.0f / sqrtf(pa_block_sum(s, red) / (float)n + eps);
+}
+
 // The seam between two sublayers of a sequential block, one CTA per token:
 //   y given:  x <- x + G(y; w_out)   (w_out null: x <- x + y)      the sublayer's output, normed, joins the residual stream
+//   add_tok / add_vec given:  x <- x + add_tok[token] + add_vec     what a new pass of a looped model adds before its first layer
 //   h given:  h  = G(x; w_in)                                       the next sublayer's input
-// G cuts the vector into `groups` equal parts and divides each by its own sqrt(mean(part^2) + eps) before the weight.
+// G cuts the vector into `groups` equal parts and divides each by its own sqrt(mean(part^2) + eps) before the weight; with
+// `center` the part's mean is taken off first (a layer norm without bias).
 __global__ void __launch_bounds__(256) pa_k_seam_norm(float *__restrict__ x, const float *__restrict__ y, const float *__restrict__ w_out, float *__restrict__ h,
-                                                      const float *__restrict__ w_in, int dim, int groups, float eps) {
+                                                      const float *__restrict__ w_in, int dim, int groups, float eps, int center, const float *__restrict__ add_tok,
+                                                      const float *__restrict__ add_vec) {
     __shared__ float red[8];
     const int64_t base = (int64_t)blockIdx.x * dim;
     const int gs = dim / groups;
     for (int g = 0; g < groups; g++) {
         const int c0 = g * gs;
         if (y) {
-            float inv = 1.0f;
-            if (w_out) {
-                float s = 0.f;
-                for (int c = threadIdx.x; c < gs; c += 256) s = fmaf(y[base + c0 + c], y[base + c0 + c], s);
-                inv = 1.0f / sqrtf(pa_block_sum(s, red) / (float)gs + eps);
-            }
-            for (int c = threadIdx.x; c < gs; c += 256) x[base + c0 + c] += w_out ? y[base + c0 + c] * inv * w_out[c0 + c] : y[base + c0 + c];
+            float inv = 1.0f, mu = 0.f;
+            if (w_out) inv = pa_block_stats(y + base + c0, gs, center, eps, red, mu);
+            for (int c = threadIdx.x; c < gs; c += 256) x[base + c0 + c] += w_out ? (y[base + c0 + c] - mu) * inv * w_out[c0 + c] : y[base + c0 + c];
         }
+        if (add_tok || add_vec)
+            for (int c = threadIdx.x; c < gs; c += 256) x[base + c0 + c] += (add_tok ? add_tok[base + c0 + c] : 0.f) + (add_vec ? add_vec[c0 + c] : 0.f);
         if (h) {
-            float s = 0.f;
-            for (int c = threadIdx.x; c < gs; c += 256) s = fmaf(x[base + c0 + c], x[base + c0 + c], s); // (a thread reads back its own writes)
-            const float inv = 1.0f / sqrtf(pa_block_sum(s, red) / (float)gs + eps);
-            for (int c = threadIdx.x; c < gs; c += 256) h[base + c0 + c] = x[base + c0 + c] * inv * w_in[c0 + c];
+            float mu;
+            const float inv = pa_block_stats(x + base + c0, gs, center, eps, red, mu); // (a thread reads back its own writes)
+            for (int c = threadIdx.x; c < gs; c += 256) h[base + c0 + c] = (x[base + c0 + c] - mu) * inv * w_in[c0 + c];
         }
     }
 }
@@ -237,15 +287,17 @@ struct PaRope {
     const double *freq; // [dims / 2]
     int dims;
     float mscale;
+    int interleaved;    // pairs (2i, 2i + 1) instead of (i, i + dims / 2)
 };
 __device__ __forceinline__ void pa_rope_store(const PaRope &r, const float *src, float *dst, int n, int pos, int c) {
     const int half = r.dims >> 1;
     if (c >= r.dims) { if (c < n) dst[c] = src[c]; return; }
-    const int i = c < half ? c : c - half;
+    const int i = r.interleaved ? c >> 1 : c < half ? c : c - half;
     const double turns = (double)pos * r.freq[i];
     const float ang = (float)fma(-rint(turns * 0.15915494309189535), 6.283185307179586, turns);
     const float cs = cosf(ang) * r.mscale, sn = sinf(ang) * r.mscale;
-    dst[c] = c < half ? src[c] * cs - src[c + half] * sn : src[c] * cs + src[c - half] * sn;
+    if (r.interleaved) dst[c] = (c & 1) == 0 ? src[c] * cs - src[c + 1] * sn : src[c] * cs + src[c - 1] * sn;
+    else dst[c] = c < half ? src[c] * cs - src[c + half] * sn : src[c] * cs + src[c - half] * sn;
 }
 
 // After the down-projections W_dq | W_dkv of a latent attention, one CTA per token.  Row t = [q latent (rq) | kv latent (rk) |
@@ -425,6 +477,14 @@ __device__ __forceinline__ float pa_expert_act(float g, float u, PaAct act) {
     return g * (1.0f / (1.0f + expf(-act.alpha * g))) * (u + act.shift);
 }
 
+// the one-argument forms (a feed-forward without a gate)
+__device__ __forceinline__ float pa_act1(float z, PaAct act) {
+    if (act.kind == PS_ACT_XIELU) return z > 0.f ? fmaf(act.alpha * z, z, 0.5f * z) : fmaf(act.shift, expm1f(z) - z, 0.5f * z);
+    if (act.kind == PS_ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    z = fminf(z, act.limit);
+    return z * (1.0f / (1.0f + expf(-act.alpha * z)));
+}
+
 // y[r][n] = act(gate_e . z_r, up_e . z_r), z_r = w_r * h[token_r] (route_on_input) or h[token_r]
 template <bool ROUND>
 __global__ void __launch_bounds__(256) pa_k_expert_up(const float *__restrict__ h, int ldh, const int *__restrict__ row_token, const float *__restrict__ row_w,
@@ -505,14 +565,38 @@ __global__ void __launch_bounds__(256) pa_k_dense_up(const float *__restrict__ h
     }
 }
 
+// feed-forward without a gate, first half: y[m][n] = act(up[n] . h_m)
+template <bool ROUND>
+__global__ void __launch_bounds__(256) pa_k_dense_up1(const float *__restrict__ h, int ldh, const bf16 *__restrict__ Wu, float *__restrict__ y, int M, int ff, int dim, PaAct act) {
+    PA_TILE_SMEM(1);
+    const int tid = threadIdx.x, lr = tid >> 2, tx = tid & 15, ty = tid >> 4;
+    const int m0 = blockIdx.y * PA_TM, n0 = blockIdx.x * PA_TN;
+    float acc[1][4][4] = {};
+    const float *arow = (m0 + lr < M) ? h + (int64_t)(m0 + lr) * ldh : nullptr;
+    pa_tile_mm<ROUND, bf16, 1>(acc, arow, 1.0f, (n0 + lr < ff) ? Wu + (int64_t)(n0 + lr) * dim : nullptr, nullptr, dim, As, Bs);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n < ff) y[(int64_t)m * ff + n] = pa_act1(acc[0][i][j], act);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------------- attention
 __device__ __forceinline__ float pa_score(const PaAttn &at, float dot, int h, int dist) {
     float s = dot * at.scale;
     if (at.temp) s *= at.temp[h];
     if (at.rel) s += at.rel[(int)at.bucket[min(dist, at.n_bucket - 1)] * at.H + h];
     if (at.r1) s -= at.r1[h] * logf(1.0f + at.r2[h] * (float)dist);
+    if (at.lin) s -= at.lin[h] * (float)dist;
     return s;
 }
+// pooled blocks a query at position p sees: those that end at or before p - window
+__device__ __forceinline__ int pa_pool_vis(const PaAttn &at, int p) { return (at.pool > 0 && p - at.window + 1 >= at.pool) ? (p - at.window + 1) / at.pool : 0; }
 // first key a query at position p sees
 __device__ __forceinline__ int pa_first_key(const PaAttn &at, int p) {
     int lo = at.window > 0 ? max(0, p - at.window + 1) : 0;
@@ -521,13 +605,36 @@ __device__ __forceinline__ int pa_first_key(const PaAttn &at, int p) {
 }
 __device__ __forceinline__ float pa_sink_logit(const PaAttn &at, int h) { return at.sink_v ? at.sink_v[h] : 0.f; }
 
-// S[h][i][j] = score of query i (position pos[i]) and cache row j <= pos[i], before the heads are mixed
+// S[h][i][j] = score of query i (position pos[i]) and cache row j <= pos[i], before the heads are mixed.  Key tiles from
+// `tok_tiles` on are tiles of pooled blocks: S[h][i][pool_off + b] = score of query i and the mean key of block b.
 __global__ void __launch_bounds__(256) pa_k_scores(PaAttn at, const float *__restrict__ qkv, int ldq, const float *__restrict__ kc, int kd, float *__restrict__ S,
-                                                   const int32_t *__restrict__ pos, int bs, int key_tile0) {
+                                                   const int32_t *__restrict__ pos, int bs, int key_tile0, int tok_tiles) {
     PA_TILE_SMEM(1);
     const int tid = threadIdx.x, lr = tid >> 2, tx = tid & 15, ty = tid >> 4;
-    const int h = blockIdx.z, g = h / (at.H / at.G), m0 = blockIdx.y * PA_TM, n0 = (blockIdx.x + key_tile0) * PA_TN;
+    const int h = blockIdx.z, g = h / (at.H / at.G), m0 = blockIdx.y * PA_TM;
     const int pos0 = pos[0], last = pos0 + min(m0 + PA_TM, bs) - 1; // the tile's furthest query
+    if ((int)blockIdx.x >= tok_tiles) {
+        const int b0 = ((int)blockIdx.x - tok_tiles) * PA_TN, nv = pa_pool_vis(at, last);
+        if (b0 >= nv) return;
+        float acc[1][4][4] = {};
+        const float *arow = (m0 + lr < bs) ? qkv + (int64_t)(m0 + lr) * ldq + h * at.dq : nullptr;
+        const float *brow = (b0 + lr < nv) ? kc + (int64_t)(at.n_ctx + b0 + lr) * kd + g * at.dq : nullptr;
+        pa_tile_mm<false, float, 1>(acc, arow, 1.0f, brow, nullptr, at.dq, As, Bs);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int m = m0 + ty * 4 + i;
+            if (m >= bs) continue;
+            const int nvm = pa_pool_vis(at, pos0 + m);
+            float *row = S + ((int64_t)h * at.B + m) * at.ldS + at.pool_off;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int b = b0 + tx * 4 + j;
+                if (b < nvm) row[b] = acc[0][i][j] * at.scale * (at.temp ? at.temp[h] : 1.0f);
+            }
+        }
+        return;
+    }
+    const int n0 = (blockIdx.x + key_tile0) * PA_TN;
     if (n0 > last || n0 + PA_TN <= pa_first_key(at, pos0 + m0)) return; // (the tile's first query sees furthest back)
     float acc[1][4][4] = {};
     const float *arow = (m0 + lr < bs) ? qkv + (int64_t)(m0 + lr) * ldq + h * at.dq : nullptr;
@@ -580,17 +687,25 @@ __global__ void __launch_bounds__(256) pa_k_mix_softmax(PaAttn at, float *__rest
         else pa_mix_rows<PA_MAX_HEADS>(at, S, i, lo, n, Ts);
         __syncthreads();
     }
+    // pooled blocks: the query's own, and those of its tile's furthest query (P.V walks whole tiles: zeros in between)
+    const int nv = pa_pool_vis(at, pos[i]), nv_tile = pa_pool_vis(at, pos[0] + min(i / PA_TM * PA_TM + PA_TM, bs) - 1);
     for (int h = warp; h < H; h += 8) {
-        float *row = S + ((int64_t)h * at.B + i) * at.ldS;
+        float *row = S + ((int64_t)h * at.B + i) * at.ldS, *prow = row + at.pool_off;
         const float sk = pa_sink_logit(at, h);
         float mx = at.sink ? sk : -INFINITY;
         for (int j = lo + lane; j < n; j += 32) mx = fmaxf(mx, row[j]);
+        for (int j = lane; j < nv; j += 32) mx = fmaxf(mx, prow[j]);
 #pragma unroll
         for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         float sum = 0.f;
         for (int j = lo + lane; j < n; j += 32) {
             const float e = expf(row[j] - mx);
             row[j] = e;
+            sum += e;
+        }
+        for (int j = lane; j < nv; j += 32) {
+            const float e = expf(prow[j] - mx);
+            prow[j] = e;
             sum += e;
         }
 #pragma unroll
@@ -600,6 +715,8 @@ __global__ void __launch_bounds__(256) pa_k_mix_softmax(PaAttn at, float *__rest
         for (int j = lo + lane; j < n; j += 32) row[j] *= inv;
         for (int j = n + lane; j < n_end; j += 32) row[j] = 0.f;
         for (int j = lo_tile + lane; j < lo; j += 32) row[j] = 0.f;
+        for (int j = lane; j < nv; j += 32) prow[j] *= inv;
+        for (int j = nv + lane; j < nv_tile; j += 32) prow[j] = 0.f;
     }
 }
 
@@ -615,6 +732,12 @@ __global__ void __launch_bounds__(256) pa_k_pv(PaAttn at, const float *__restric
     const float *arow = (m0 + lr < bs) ? S + ((int64_t)h * at.B + m0 + lr) * at.ldS + k0 : nullptr;
     const float *brow = (n0 + lr < at.dv) ? vct + (int64_t)(g * at.dv + n0 + lr) * at.n_ctx + k0 : nullptr;
     pa_tile_mm<false, float, 1>(acc, arow, 1.0f, brow, nullptr, n_keys - k0, As, Bs);
+    const int nv = pa_pool_vis(at, n_keys - 1); // pooled blocks of the tile's furthest query: their weights times the mean value rows
+    if (nv > 0) {
+        const float *arow2 = (m0 + lr < bs) ? S + ((int64_t)h * at.B + m0 + lr) * at.ldS + at.pool_off : nullptr;
+        const float *brow2 = (n0 + lr < at.dv) ? vct + (int64_t)at.G * at.dv * at.n_ctx + (int64_t)(g * at.dv + n0 + lr) * at.n_pool : nullptr;
+        pa_tile_mm<false, float, 1>(acc, arow2, 1.0f, brow2, nullptr, nv, As, Bs);
+    }
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int m = m0 + ty * 4 + i;

@@ -70,9 +70,9 @@ __global__ void __launch_bounds__(256) pa_k_conv_step(const float *__restrict__ 
     y[c] = act_silu ? pa_silu(acc) : acc;
 }
 
-// one CTA per token; row = [q (qd) | k (kd) | v (vd)]
+// one CTA per token; row = [q (qd) | k (kd) | ...], the value rows from v_off on (at the keys when the values are the un-normed keys)
 __global__ void __launch_bounds__(256) pa_k_qkv_whole_norm(float *__restrict__ qkv, int ld, int qd, int kd, int vd, const float *__restrict__ wq, const float *__restrict__ wk,
-                                                           float eps, float *__restrict__ kc, float *__restrict__ vct, int n_ctx, const int32_t *__restrict__ pos) {
+                                                           float eps, float *__restrict__ kc, float *__restrict__ vct, int n_ctx, const int32_t *__restrict__ pos, int v_off) {
     __shared__ float red[8];
     const int t = blockIdx.x, p = pos[t];
     float *row = qkv + (int64_t)t * ld;
@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(256) pa_k_qkv_whole_norm(float *__restrict__ q
     for (int c = threadIdx.x; c < kd; c += 256) s = fmaf(row[qd + c], row[qd + c], s);
     const float ik = 1.0f / sqrtf(pa_block_sum(s, red) / (float)kd + eps);
     for (int c = threadIdx.x; c < kd; c += 256) kc[(int64_t)p * kd + c] = row[qd + c] * ik * wk[c];
-    for (int c = threadIdx.x; c < vd; c += 256) vct[(int64_t)c * n_ctx + p] = row[qd + kd + c];
+    for (int c = threadIdx.x; c < vd; c += 256) vct[(int64_t)c * n_ctx + p] = row[v_off + c];
 }
 
 // grid (entries / 256, tokens); n_heads heads of hd entries from v[t * ld] on; heads h >= h_scaled are multiplied by `scale` after the rotation
@@ -104,6 +104,39 @@ __global__ void __launch_bounds__(256) pa_k_rope_heads(float *__restrict__ v, in
         x[c] = (a * cs - b * sn) * sc;
         x[c + half] = (b * cs + a * sn) * sc;
     }
+}
+
+// What follows an attention that has an output gate and / or a minGRU beside it, on the rows of the first projection
+// [.. | gate (od) | z (W) | u (W) | side gate (W)]:
+//   CTAs below gate_ctas (grid.y walks the tokens): att[t][c] <- att[t][c] * sigmoid(gate[t][c]) * mix_scale
+//   the others (blockIdx.y = 0 only), a thread per channel, tokens strictly in order:  z = sigmoid(z_raw + bz), u = u_raw + bx,
+//   cand = u + 1/2 (u >= 0) or sigmoid(u) (u < 0), S <- (1 - z) S + z cand  (S = 0 at position 0 whatever the buffer holds),
+//   att[t][od + c] = S * silu(side gate) * side_scale.
+// The next product reads att rows of od + W entries against [W_o | W_side_o].
+__global__ void __launch_bounds__(128) pa_k_gate_gru(float *__restrict__ att, int ldo, const float *__restrict__ proj, int ld, int od, int g_off, float mix_scale, int gate_ctas,
+                                                     int W, int z_off, const float *__restrict__ bz, const float *__restrict__ bx, float side_scale,
+                                                     float *__restrict__ state, const int32_t *__restrict__ pos, int bs) {
+    if ((int)blockIdx.x < gate_ctas) {
+        const int c = blockIdx.x * 128 + threadIdx.x;
+        if (c >= od) return;
+        for (int t = blockIdx.y; t < bs; t += gridDim.y) {
+            const float g = g_off >= 0 ? 1.0f / (1.0f + expf(-proj[(int64_t)t * ld + g_off + c])) : 1.0f;
+            att[(int64_t)t * ldo + c] *= g * mix_scale;
+        }
+        return;
+    }
+    const int c = ((int)blockIdx.x - gate_ctas) * 128 + threadIdx.x;
+    if (blockIdx.y != 0 || c >= W) return;
+    float S = pos[0] > 0 ? state[c] : 0.f;
+    const float b0 = bz[c], b1 = bx[c];
+    for (int t = 0; t < bs; t++) {
+        const float *row = proj + (int64_t)t * ld + z_off;
+        const float z = 1.0f / (1.0f + expf(-(row[c] + b0))), u = row[W + c] + b1;
+        const float cand = u >= 0.f ? u + 0.5f : 1.0f / (1.0f + expf(-u));
+        S = (1.0f - z) * S + z * cand;
+        att[(int64_t)t * ldo + od + c] = S * pa_silu(row[2 * W + c]) * side_scale;
+    }
+    state[c] = S;
 }
 
 #define PA_SC_TOK 32    // tokens staged per round (half as many for the widest states)

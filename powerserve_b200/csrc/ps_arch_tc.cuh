@@ -81,6 +81,7 @@ struct PtArgs {
     const float *row_w;
     int top, on_input;
     PaAct act;
+    int act1;               // PT_MODE_DENSE: the one-argument activation on every output (a feed-forward without a gate)
     int *err;
 };
 
@@ -192,7 +193,7 @@ __global__ void __launch_bounds__(PT_THREADS, 1) pa_k_tc_gemm(const PtArgs a) {
                         if (r >= rend) break;
                         const float acc = __uint_as_float(v[c]);
                         if (a.mode == PT_MODE_DENSE) {
-                            a.C[(int64_t)r * a.ldc + n] = acc + bias;
+                            a.C[(int64_t)r * a.ldc + n] = a.act1 ? pa_act1(acc + bias, a.act) : acc + bias;
                         } else if (a.mode == PT_MODE_EXPERT_UP) {
                             a.C[(int64_t)r * a.ldc + n] = pa_expert_act(acc, NA == 2 ? __uint_as_float(w2[c]) : 0.f, a.act);
                         } else {
