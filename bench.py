@@ -308,7 +308,7 @@ def main():
     ap.add_argument("--tp-nccl", action="store_true", help="tensor parallel with NCCL all-gathers instead of the fused peer-store kernels")
     ap.add_argument("--replicas", action="store_true", help="N > 1: independent replicas instead of tensor parallelism")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary legs (1B config, speculative config, PowerServe-stack e2e)")
-    ap.add_argument("--arch", default="", choices=["", "nufusun", "vanapel", "dozotar"],
+    ap.add_argument("--arch", default="", choices=["", "nufusun", "vanapel", "dozotar", "pidenex"],
                     help="instead of the default workload: prefill / decode throughput of a layer-list design at real layer sizes, beside the closest existing model")
     ap.add_argument("--arch-sizes", default="s,m,l")
     ap.add_argument("--arch-prompt", type=int, default=2048)

@@ -1,4 +1,4 @@
-"""bench.py --arch nufusun | vanapel | dozotar: prefill and decode throughput of a layer-list design at layer sizes that resemble real
+"""bench.py --arch nufusun | vanapel | dozotar | pidenex: prefill and decode throughput of a layer-list design at layer sizes that resemble real
 models (random weights), beside the closest existing model of the framework.
 
 --arch vanapel: the Vanapel design (windowed attention layers and one latent-attention layer, dense gated feed-forward) beside
@@ -7,6 +7,12 @@ ff = ff) - the same executor, kernels and bfloat16 weights, so the two steps mov
 
 --arch dozotar: the Dozotar design (retention, state-space and chunked-attention layers; dense gelu and routed feed-forwards with a
 shared expert) beside Nufusun at equal width, attention head geometry, layer count, vocabulary and ACTIVE feed-forward rows per token.
+
+--arch pidenex: the Pidenex design (pooled-window attention whose values are its keys, a gated attention beside a minGRU, latent
+attention with rotation in neighbouring pairs, feed-forwards without a gate; the first two layers run twice with the same weights at
+sizes s and m) beside Vanapel - the closest existing model: sequential blocks normed on both sides, windowed and latent attention,
+dense feed-forward - with as many layer runs, equal width, head geometry, windows, vocabulary and feed-forward bytes (a gated unit of
+ff rows against an ungated one of 3 ff / 2).
 
 --arch nufusun: prefill and decode throughput of the Nufusun design at layer sizes that resemble real models
 (random weights), beside the closest existing model of the framework - a llama stack (Q4_K) with the same width, head
@@ -263,6 +269,75 @@ def run_size_dozotar(name, prompt_len, steps, warmup, seed, chunk):
     return out
 
 
+# name: (width, heads, kv heads, head size, window, pool, minGRU channels, gated-equivalent ff, latent geometry, layer types, loop, vocab)
+PIDENEX_SIZES = {
+    "s": (1024, 16, 4, 64, 512, 16, 512, 2048, (16, 64, 32, 64, 384, 256), "apl", (0, 2, 2), 32000),
+    "m": (2048, 16, 4, 128, 1024, 16, 1024, 5632, (16, 128, 64, 128, 768, 512), "apl", (0, 2, 2), 32000),
+    "l": (4096, 32, 8, 128, 1024, 16, 2048, 14336, (32, 128, 64, 128, 1536, 512), "apl", None, 32000),
+}
+
+
+def run_size_pidenex(name, prompt_len, steps, warmup, seed, chunk):
+    W, H, G, hs, win, pool, R, ff, (LH, dn, dr, dv, rq, rk), kinds, loop, V = PIDENEX_SIZES[name]
+    hbm, tflops, src = _peaks()
+    n_ctx = -(-(prompt_len + steps + warmup + 24) // 256) * 256
+    prompt = [int(v) for v in np.random.default_rng(1234).integers(0, V, prompt_len)]
+    ffp = 3 * ff // 2                                                # up and down rows of an ungated unit: the bytes of a gated unit of ff rows
+    out = {"size": name, "width": W, "heads": [H, G], "head_size": hs, "window": win, "pool": pool, "gru": R, "ff": ffp, "latent": [LH, dn, dr, dv, rq, rk],
+           "layers": kinds, "loop": loop, "vocab": V, "context": prompt_len}
+    layers = []
+    for k in kinds:
+        if k == "a":
+            layers.append(arch_synth.pidenex_attention_layer(H, G, hs, window=win, pool=pool, ff=ffp))
+        elif k == "p":
+            layers.append(arch_synth.pidenex_parallel_layer(H, G, hs, window=win, gru_width=R, ff=ffp))
+        else:
+            layers.append(arch_synth.pidenex_latent_layer(LH, dn, dr, dv, rq, rk, window=win, rope_base=5e5, ff=ffp))
+    cfg = arch_synth.pidenex_config(W, V, layers, loop=loop, embed_scale=2.0)
+    m = _load_synth(cfg, arch_synth.pidenex_weights(cfg, seed=seed, fast=True), chunk, n_ctx)
+    t_pre, t_dec, launches, e2e = _measure(m, prompt, chunk, steps, warmup)
+    m.close()
+    runs = "".join(kinds[i] for i, _ in arch._pidenex_runs(cfg))
+    na, npar, nlat = runs.count("a"), runs.count("p"), runs.count("l")
+    p_att = (H + G) * hs * W + H * hs * W
+    p_par = (H + G) * hs * W + 2 * H * hs * W + 4 * R * W
+    p_lat = (rq + rk + dr) * W + LH * (dn + dr) * rq + LH * dn * rk + LH * dv * rk + LH * dv * W
+    act_params = na * p_att + npar * p_par + nlat * p_lat + len(runs) * 2 * ffp * W + V * W   # every run streams its weights, shared or not
+    keys = min(win, prompt_len)
+    blocks = max(0, prompt_len - win) // pool
+    kv_bytes = (na + npar) * 2 * G * hs * 4 * keys + na * 2 * G * hs * 4 * blocks + npar * 2 * R * 4 + nlat * (2 * rk + dr) * 4 * keys
+    mix_flops = (na + npar) * 2 * 2 * H * hs * min(win, prompt_len / 2) + na * 2 * 2 * H * hs * blocks / 2 + nlat * 2 * LH * (2 * rk + dr) * min(win, prompt_len / 2)
+    out["pidenex"] = {
+        "runs": runs, "prefill_tok_s": prompt_len / t_pre, "prefill_chunk": chunk,
+        "prefill_tflops": (2 * act_params + mix_flops) * prompt_len / t_pre / 1e12,
+        "prefill_frac_of_bf16_peak": (2 * act_params + mix_flops) * prompt_len / t_pre / 1e12 / tflops,
+        "decode_tok_s": 1 / t_dec, "decode_ms": t_dec * 1e3, "decode_launches_per_step": launches,
+        "decode_bytes_per_token": 2 * act_params + kv_bytes, "decode_frac_of_hbm_peak": (2 * act_params + kv_bytes) / t_dec / 1e9 / hbm,
+        "e2e_decode_tok_s": e2e}
+
+    # ---- the closest existing model: Vanapel with a layer per run (the parallel layer's place taken by a windowed attention layer)
+    vkinds = runs.replace("p", "a")
+    vlayers = [arch_synth.vanapel_attention_layer(H, G, hs, hs, window=win, ff=ff, limit=7.0) if k == "a" else
+               arch_synth.vanapel_latent_layer(LH, dn, dr, dv, rq, rk, rope_base=5e5, ff=ff, limit=7.0) for k in vkinds]
+    vcfg = arch_synth.vanapel_config(W, V, vlayers, groups=1)
+    m = _load_synth(vcfg, arch_synth.vanapel_weights(vcfg, seed=seed, fast=True), chunk, n_ctx)
+    t_pre_v, t_dec_v, launches_v, e2e_v = _measure(m, prompt, chunk, steps, warmup)
+    m.close()
+    va, vl = vkinds.count("a"), vkinds.count("l")
+    v_params = va * ((H + 2 * G) * hs * W + H * hs * W) + vl * p_lat + len(vkinds) * 3 * ff * W + V * W
+    v_kv = va * 2 * G * hs * 4 * keys + vl * (2 * rk + dr) * 4 * prompt_len
+    v_flops = va * 2 * 2 * H * hs * min(win, prompt_len / 2) + vl * 2 * LH * (2 * rk + dr) * prompt_len / 2
+    out["vanapel"] = {
+        "layers": vkinds, "prefill_tok_s": prompt_len / t_pre_v, "prefill_chunk": chunk,
+        "prefill_tflops": (2 * v_params + v_flops) * prompt_len / t_pre_v / 1e12,
+        "prefill_frac_of_bf16_peak": (2 * v_params + v_flops) * prompt_len / t_pre_v / 1e12 / tflops,
+        "decode_tok_s": 1 / t_dec_v, "decode_ms": t_dec_v * 1e3, "decode_launches_per_step": launches_v,
+        "decode_bytes_per_token": 2 * v_params + v_kv, "decode_frac_of_hbm_peak": (2 * v_params + v_kv) / t_dec_v / 1e9 / hbm,
+        "e2e_decode_tok_s": e2e_v}
+    out["peaks"] = {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": src}
+    return out
+
+
 def main(args) -> int:
     if capi.load_library().ps_cuda_device_count() == 0:
         print(json.dumps({"arch": args.arch, "unavailable": "no CUDA device: there is no CPU fallback"}))
@@ -271,6 +346,11 @@ def main(args) -> int:
     if args.arch == "dozotar":
         res = [run_size_dozotar(s, args.arch_prompt, max(args.steps, 8), max(args.warmup, 3), args.seed, args.arch_chunk) for s in sizes]
         print(json.dumps({"arch": "dozotar", "dtype": "bf16", "data": "synthetic", "timing": "CUDA events around every call, warm-up first; weights exceed L2",
+                          "sizes": res}))
+        return 0
+    if args.arch == "pidenex":
+        res = [run_size_pidenex(s, args.arch_prompt, max(args.steps, 8), max(args.warmup, 3), args.seed, args.arch_chunk) for s in sizes]
+        print(json.dumps({"arch": "pidenex", "dtype": "bf16", "data": "synthetic", "timing": "CUDA events around every call, warm-up first; weights exceed L2",
                           "sizes": res}))
         return 0
     if args.arch == "vanapel":

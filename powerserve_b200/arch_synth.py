@@ -246,3 +246,87 @@ def dozotar_weights(cfg: dict, seed: int = 0, rel_rows: int = 16, fast: bool = F
                     t[p + "mlp.shared." + f] = a
                 t[p + "mlp.shared.sg"] = mat(1, W, 2.0)
     return t
+
+
+# ------------------------------------------------------------------------------------------------------------ Pidenex
+def _pidenex_mlp(ff: int) -> Optional[dict]:
+    return {"kind": "dense", "ff": ff} if ff else None
+
+
+def pidenex_attention_layer(heads: int, kv_heads: int, dim: int, *, window: int, pool: int = 0, scale: Optional[float] = None, ff: int = 0) -> dict:
+    """a windowed attention whose values are its keys (vdim = dim); pool > 0 adds the mean key per block of `pool` tokens before the window"""
+    mask = {"size": window}
+    if pool:
+        mask["pool"] = pool
+    return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "mask": mask, "scale": float(scale if scale is not None else dim ** -0.5)},
+            "mlp": _pidenex_mlp(ff)}
+
+
+def pidenex_parallel_layer(heads: int, kv_heads: int, dim: int, *, window: int, gru_width: int, left_scale: float = 0.8, right_scale: float = 0.9,
+                           scale: Optional[float] = None, ff: int = 0) -> dict:
+    """a gated attention with a linear distance penalty beside a minGRU of gru_width channels"""
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "mask": {"size": window}, "scale": float(scale if scale is not None else dim ** -0.5)}
+    return {"type": "parallel", "mixer": {"left": left, "left_scale": left_scale, "right": {"width": gru_width}, "right_scale": right_scale}, "mlp": _pidenex_mlp(ff)}
+
+
+def pidenex_latent_layer(heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int, kv_rank: int, *, window: int = 0, scale: Optional[float] = None,
+                         rope_base: float = 10000.0, ff: int = 0) -> dict:
+    mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "rot": {"base": rope_base, "dims": rot_dim},
+             "scale": float(scale if scale is not None else (dim + rot_dim) ** -0.5)}
+    if window:
+        mixer["mask"] = {"size": window}
+    return {"type": "latent_attention", "mixer": mixer, "mlp": _pidenex_mlp(ff)}
+
+
+def pidenex_config(width: int, vocab: int, layers: List[dict], *, loop: Optional[tuple] = None, eps: float = 1e-6, embed_scale: float = 1.0) -> dict:
+    """loop = (start, stop, times): the layers start .. stop - 1 run `times` times with the same weights"""
+    a, b, n = loop if loop else (0, 0, 1)
+    return {"architecture": "Pidenex", "embedding": {"scale": embed_scale}, "layers": layers, "loop": {"start": a, "stop": b, "times": n}, "norm": {"eps": eps},
+            "vocab": vocab, "width": width}
+
+
+def pidenex_weights(cfg: dict, seed: int = 0, fast: bool = False) -> Dict[str, np.ndarray]:
+    """float32 arrays of bfloat16-representable values keyed by tensor name (fast = True: big matrices as random bfloat16 bit patterns)"""
+    rng = np.random.default_rng(seed)
+    W, V = cfg["width"], cfg["vocab"]
+
+    def rnd(a):
+        return (safetensors.float32_to_bf16_bits(np.asarray(a, np.float32)).astype(np.uint32) << 16).view(np.float32)
+
+    def mat(out_dim, in_dim, gain=1.0):
+        if fast:
+            e = int(np.floor(np.log2(gain / np.sqrt(in_dim)))) + 127
+            bits = rng.integers(0, 1 << 7, size=(out_dim, in_dim), dtype=np.uint16) | np.uint16(e << 7)
+            return bits | (rng.integers(0, 2, size=(out_dim, in_dim), dtype=np.uint16) << 15).astype(np.uint16)
+        return rnd(rng.standard_normal((out_dim, in_dim), dtype=np.float32) * np.float32(gain / np.sqrt(in_dim)))
+
+    def vec(n, mean=0.0, dev=0.1):
+        return rnd(mean + rng.standard_normal(n).astype(np.float32) * dev)
+
+    t: Dict[str, np.ndarray] = {"embed": mat(V, W, np.sqrt(W)), "final.norm": vec(W, 1.0), "head": mat(V, W)}
+    lp = cfg.get("loop") or {}
+    if lp.get("stop", 0) > lp.get("start", 0):
+        t["loop.step"] = rnd(rng.standard_normal((lp["times"], W)).astype(np.float32) * 0.5)
+    for i, l in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", l["mixer"]
+        t[p + "norm1"], t[p + "norm1b"] = vec(W, 1.0), vec(W, 0.5)
+        if l["type"] == "attention":
+            H, G, dq = m["heads"], m["kv_heads"], m["dim"]
+            t[p + "mix.q"], t[p + "mix.k"], t[p + "mix.o"] = mat(H * dq, W, 2.0), mat(G * dq, W, 2.0), mat(W, H * dq)
+        elif l["type"] == "parallel":
+            a, b, ml, R = p + "mix.left.", p + "mix.right.", m["left"], m["right"]["width"]
+            H, G, dq = ml["heads"], ml["kv_heads"], ml["dim"]
+            t[a + "q"], t[a + "k"], t[a + "g"], t[a + "o"] = mat(H * dq, W, 2.0), mat(G * dq, W, 2.0), mat(H * dq, W, 2.0), mat(W, H * dq)
+            t[a + "q.norm"], t[a + "k.norm"] = vec(H * dq, 1.0, 0.2), vec(G * dq, 1.0, 0.2)
+            t[b + "z"], t[b + "x"], t[b + "g"], t[b + "o"] = mat(R, W, 2.0), mat(R, W, 2.0), mat(R, W, 2.0), mat(W, R)
+            t[b + "z.b"], t[b + "x.b"] = vec(R, 0.0, 0.5), vec(R, 0.0, 0.5)
+        else:
+            H, dn, dr, dv, rq, rk = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["q_rank"], m["kv_rank"]
+            t[p + "mix.dq"], t[p + "mix.dq.norm"], t[p + "mix.uq"] = mat(rq, W), vec(rq, 1.0), mat(H * (dn + dr), rq, 2.0)
+            t[p + "mix.dkv"], t[p + "mix.dkv.norm"] = mat(rk + dr, W, 2.0), vec(rk, 1.0)
+            t[p + "mix.uk"], t[p + "mix.uv"], t[p + "mix.o"] = mat(H * dn, rk, 2.0), mat(H * dv, rk), mat(W, H * dv)
+        if l.get("mlp") is not None:
+            ff = l["mlp"]["ff"]
+            t[p + "norm2"], t[p + "norm2b"] = vec(W, 1.0), vec(W, 0.5)
+            t[p + "mlp.up"], t[p + "mlp.down"], t[p + "mlp.act"] = mat(ff, W, 1.5), mat(W, ff), rnd(rng.standard_normal(2).astype(np.float32))
+    return t

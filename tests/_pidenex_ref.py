@@ -13,6 +13,13 @@ import numpy as np
 
 
 # ------------------------------------------------------------------------------------------------------------ small pieces
+def bf16_round(a):
+    """round to the nearest bfloat16 value (ties to even), returned as float32"""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32).reshape(np.shape(a))
+
+
 def layer_norm(x, w, eps):
     """(x - mean) / sqrt(var + eps) * w over the last axis; var = mean of squared deviations; no bias"""
     mu = x.mean(-1, keepdims=True)
@@ -216,6 +223,7 @@ def layer(x, l, W, i, eps):
 def forward(cfg, W, tokens, taps=None):
     """tokens [T] -> logits [T, vocab]; taps (a list) receives the residual stream after every layer run"""
     eps = cfg["norm"]["eps"]
+    W = {k: np.asarray(v, np.float64) for k, v in W.items()}
     x0 = W["embed"][np.asarray(tokens)] * cfg["embedding"]["scale"]
     x = x0
     for i, t in layer_runs(cfg):
