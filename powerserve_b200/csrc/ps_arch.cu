@@ -1093,8 +1093,8 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             else rc = attend(at, q, w.pw, w.kd, li, w.aw);
             if (rc) return rc;
             if (l.out_gate || l.side_kind) { // the heads' outputs through their gate; the side mixer's recurrence fills the columns behind them
-                const unsigned gate_ctas = cdiv(w.ho, 128), side_ctas = l.side_kind ? cdiv(l.side_width, 128) : 0;
-                pa_k_gate_gru<<<dim3(gate_ctas + side_ctas, (unsigned)std::min(bs, 64)), 128, 0, st>>>(a->att, w.aw, a->qkv, w.pw, w.ho, l.out_gate ? w.g_off : -1, l.side_kind ? l.mix_scale : 1.0f,
+                const unsigned gate_ctas = cdiv(w.ho, PA_GG_THREADS), side_ctas = l.side_kind ? cdiv(l.side_width, 32) : 0;
+                pa_k_gate_gru<<<dim3(gate_ctas + side_ctas, (unsigned)std::min(bs, 64)), PA_GG_THREADS, 0, st>>>(a->att, w.aw, a->qkv, w.pw, w.ho, l.out_gate ? w.g_off : -1, l.side_kind ? l.mix_scale : 1.0f,
                                                                                                      (int)gate_ctas, l.side_kind ? l.side_width : 0, w.z_off, w.side_b, l.side_kind ? w.side_b + l.side_width : nullptr,
                                                                                                      l.side_scale, io.kc[li] + w.state_off, io.pos_dev, bs);
                 PA_LAUNCH();

@@ -106,14 +106,16 @@ __global__ void __launch_bounds__(256) pa_k_rope_heads(float *__restrict__ v, in
     }
 }
 
+#define PA_GG_THREADS 128
+#define PA_GG_TOK 32      // tokens per round of the side mixer's scan
 // What follows an attention that has an output gate and / or a minGRU beside it, on the rows of the first projection
 // [.. | gate (od) | z (W) | u (W) | side gate (W)]:
 //   CTAs below gate_ctas (grid.y walks the tokens): att[t][c] <- att[t][c] * sigmoid(gate[t][c]) * mix_scale
-//   the others (blockIdx.y = 0 only), a thread per channel, tokens strictly in order:  z = sigmoid(z_raw + bz), u = u_raw + bx,
+//   the others (blockIdx.y = 0 only; 32 channels each), tokens strictly in order:  z = sigmoid(z_raw + bz), u = u_raw + bx,
 //   cand = u + 1/2 (u >= 0) or sigmoid(u) (u < 0), S <- (1 - z) S + z cand  (S = 0 at position 0 whatever the buffer holds),
 //   att[t][od + c] = S * silu(side gate) * side_scale.
 // The next product reads att rows of od + W entries against [W_o | W_side_o].
-__global__ void __launch_bounds__(128) pa_k_gate_gru(float *__restrict__ att, int ldo, const float *__restrict__ proj, int ld, int od, int g_off, float mix_scale, int gate_ctas,
+__global__ void __launch_bounds__(PA_GG_THREADS) pa_k_gate_gru(float *__restrict__ att, int ldo, const float *__restrict__ proj, int ld, int od, int g_off, float mix_scale, int gate_ctas,
                                                      int W, int z_off, const float *__restrict__ bz, const float *__restrict__ bx, float side_scale,
                                                      float *__restrict__ state, const int32_t *__restrict__ pos, int bs) {
     if ((int)blockIdx.x < gate_ctas) {
@@ -125,18 +127,44 @@ __global__ void __launch_bounds__(128) pa_k_gate_gru(float *__restrict__ att, in
         }
         return;
     }
-    const int c = ((int)blockIdx.x - gate_ctas) * 128 + threadIdx.x;
-    if (blockIdx.y != 0 || c >= W) return;
-    float S = pos[0] > 0 ? state[c] : 0.f;
-    const float b0 = bz[c], b1 = bx[c];
-    for (int t = 0; t < bs; t++) {
-        const float *row = proj + (int64_t)t * ld + z_off;
-        const float z = 1.0f / (1.0f + expf(-(row[c] + b0))), u = row[W + c] + b1;
-        const float cand = u >= 0.f ? u + 0.5f : 1.0f / (1.0f + expf(-u));
-        S = (1.0f - z) * S + z * cand;
-        att[(int64_t)t * ldo + od + c] = S * pa_silu(row[2 * W + c]) * side_scale;
+    // 32 channels per CTA, rounds of 32 tokens: the four warps take eight tokens each, fetch their operands and form the gates side by
+    // side into shared memory (nothing there depends on S); then warp 0 walks the 32 steps in order, a lane per channel - the same
+    // operations per step whatever the round, so the result does not depend on how the prompt was cut
+    __shared__ float za[PA_GG_TOK][32], ca[PA_GG_TOK][32], ga[PA_GG_TOK][32];
+    if (blockIdx.y != 0) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, c = ((int)blockIdx.x - gate_ctas) * 32 + lane;
+    const bool live = c < W;
+    float S = (live && pos[0] > 0) ? state[c] : 0.f;
+    const float b0 = live ? bz[c] : 0.f, b1 = live ? bx[c] : 0.f;
+    constexpr int PER = PA_GG_TOK / (PA_GG_THREADS / 32);
+    for (int t0 = 0; t0 < bs; t0 += PA_GG_TOK) {
+        float zr[PER], ur[PER], gr[PER];
+#pragma unroll
+        for (int i = 0; i < PER; i++) {
+            const int t = t0 + warp * PER + i;
+            const float *row = proj + (int64_t)min(t, bs - 1) * ld + z_off;
+            zr[i] = live ? row[c] : 0.f; ur[i] = live ? row[W + c] : 0.f; gr[i] = live ? row[2 * W + c] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < PER; i++) {
+            const float u = ur[i] + b1;
+            za[warp * PER + i][lane] = 1.0f / (1.0f + expf(-(zr[i] + b0)));
+            ca[warp * PER + i][lane] = u >= 0.f ? u + 0.5f : 1.0f / (1.0f + expf(-u));
+            ga[warp * PER + i][lane] = pa_silu(gr[i]) * side_scale;
+        }
+        __syncthreads();
+        if (warp == 0 && live) {
+            const int n = min(PA_GG_TOK, bs - t0);
+#pragma unroll 8
+            for (int i = 0; i < n; i++) {
+                const float z = za[i][lane];
+                S = (1.0f - z) * S + z * ca[i][lane];
+                att[(int64_t)(t0 + i) * ldo + od + c] = S * ga[i][lane];
+            }
+        }
+        __syncthreads();
     }
-    state[c] = S;
+    if (warp == 0 && live) state[c] = S;
 }
 
 #define PA_SC_TOK 32    // tokens staged per round (half as many for the widest states)
