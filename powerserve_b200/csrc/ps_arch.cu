@@ -842,12 +842,13 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         return 0;
     };
     // scores and P.V of one query against the cache; the grids do not depend on the position (a window bounds the blocks of keys)
-    auto attend_single = [&](const PaAttn &at, const float *q, int li) -> int {
+    auto attend_single = [&](const PaAttn &at, const float *q, int li, bool pool_here = false) -> int {
         unsigned blocks = cdiv(n_kv_cap, PA_DS_KEYS);
         if (at.window > 0) blocks = std::min(blocks, cdiv(at.window, PA_DS_KEYS) + 1);
         if (at.chunk > 0) blocks = std::min(blocks, cdiv(at.chunk, PA_DS_KEYS) + 1);
         const unsigned pooled = at.pool > 0 ? cdiv(n_kv_cap / at.pool, PA_DS_KEYS) : 0; // further CTAs for the pooled blocks
-        pa_launch_dep(pdl, pa_k_dec_scores, dim3(blocks + pooled), dim3(256), pa_dec_scores_smem(at.H, at.G, at.dq), st, at, q, (const float *)io.kc[li], io.pos_dev, a->S, io.err_dev, (int)blocks);
+        pa_launch_dep(pdl, pa_k_dec_scores, dim3(blocks + pooled), dim3(256), pa_dec_scores_smem(at.H, at.G, at.dq), st, at, q, (const float *)io.kc[li], io.pos_dev, a->S, io.err_dev, (int)blocks,
+                      pool_here && pooled ? io.vct[li] : (float *)nullptr);
         PA_LAUNCH();
         pa_launch_dep(pdl, pa_k_dec_pv, dim3(cdiv(at.dv, PA_DP_DIMS), at.G, pa_dec_pv_split(at.H, at.G)), dim3(256), pa_dec_pv_smem(at.H, at.G), st, at, (const float *)a->S, (const float *)io.vct[li], io.pos_dev, a->att,
                       pa_dec_pv_chunk(at.H, at.G), io.err_dev);
@@ -1050,10 +1051,15 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         const int H = l.n_heads;
         const bool raw = l.raw_input != 0;
         int rc;
+        // single token, attention without convolution or q / k norm: the K rows (and V rows) go from the mat-vec straight into the cache
+        const bool direct = single && l.mixer_kind == PS_MIXER_ATTENTION && l.conv_taps == 0 && l.qk_norm == PS_QKNORM_NONE;
         if (single) {
             PaMv mv{};
             seam_mv(mv, raw ? nullptr : w.norm);
             mv.W = w.wqkv; mv.N = w.pw; mv.K = dim; mv.y = a->qkv;
+            if (direct) {
+                mv.qd = w.qd; mv.kd = w.kd; mv.vd = l.v_is_k ? 0 : w.vd; mv.v_is_k = l.v_is_k; mv.kc = io.kc[li]; mv.vct = io.vct[li]; mv.n_ctx = d.n_ctx; mv.pos = io.pos_dev;
+            }
             if ((rc = dec_mv(mv, 4 * (size_t)dim))) return rc;
         } else {
             if ((rc = seam(raw ? nullptr : a->h, raw ? nullptr : w.norm))) return rc;
@@ -1075,12 +1081,14 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
                 PA_LAUNCH();
                 q = a->cv;
             }
-            if (l.qk_norm == PS_QKNORM_WHOLE)
+            if (l.qk_norm == PS_QKNORM_WHOLE) {
                 pa_k_qkv_whole_norm<<<bs, 256, 0, st>>>(q, w.pw, w.qd, w.kd, w.vd, w.q_norm, w.k_norm, d.norm_eps, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev, w.v_off);
-            else
+                PA_LAUNCH();
+            } else if (!direct) {
                 pa_k_kv_store<<<dim3(cdiv(w.kd + w.vd, 256), bs), 256, 0, st>>>(q, w.pw, w.qd, w.kd, w.vd, io.kc[li], io.vct[li], d.n_ctx, io.pos_dev, w.v_off);
-            PA_LAUNCH();
-            if (l.pool > 0) { // the means of the blocks that this batch completes (at most bs / pool + 1 of them)
+                PA_LAUNCH();
+            }
+            if (l.pool > 0 && !single) { // the means of the blocks that this batch completes (at most bs / pool + 1 of them); a single token's scores kernel forms its own
                 pa_k_pool_blocks<<<dim3(cdiv(w.kd + w.vd, 256), (unsigned)(bs / l.pool + 1)), 256, 0, st>>>(io.kc[li], io.vct[li], w.kd, w.vd, d.n_ctx, l.pool, w.n_pool, io.pos_dev, bs);
                 PA_LAUNCH();
             }
@@ -1089,7 +1097,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
             at.sink = l.sink != PS_SINK_NONE; at.sink_v = w.sink_v; at.r1 = w.r1; at.r2 = w.r2; at.window = l.window; at.chunk = l.chunk;
             at.n_ctx = d.n_ctx; at.ldS = a->ldS; at.B = B; at.pm = a->pm; at.pl = a->pl; at.ldP = a->ldP;
             at.lin = w.lin; at.pool = l.pool; at.n_pool = w.n_pool; at.pool_off = a->pool_off; at.stat_off = a->stat_off;
-            if (single) rc = attend_single(at, q, li);
+            if (single) rc = attend_single(at, q, li, true);
             else rc = attend(at, q, w.pw, w.kd, li, w.aw);
             if (rc) return rc;
             if (l.out_gate || l.side_kind) { // the heads' outputs through their gate; the side mixer's recurrence fills the columns behind them
@@ -1255,7 +1263,7 @@ static int forward_t(PsArch *a, const PsArchIO &io, int bs, int pos0, int lm_hea
         at.H = H; at.G = G; at.dq = dq; at.dv = dv; at.scale = l.score_scale; at.temp = w.temp; at.rel = w.rel; at.bucket = w.bucket; at.n_bucket = d.n_ctx;
         at.mix = w.mix; at.sink = l.sink != PS_SINK_NONE; at.n_ctx = d.n_ctx; at.ldS = a->ldS; at.B = B; at.pm = a->pm; at.pl = a->pl; at.ldP = a->ldP;
         if (single) {
-            pa_launch_dep(pdl, pa_k_dec_scores, dim3(cdiv(n_kv_cap, PA_DS_KEYS)), dim3(256), pa_dec_scores_smem(H, G, dq), st, at, (const float *)a->qkv, (const float *)io.kc[li], io.pos_dev, a->S, io.err_dev, (int)cdiv(n_kv_cap, PA_DS_KEYS));
+            pa_launch_dep(pdl, pa_k_dec_scores, dim3(cdiv(n_kv_cap, PA_DS_KEYS)), dim3(256), pa_dec_scores_smem(H, G, dq), st, at, (const float *)a->qkv, (const float *)io.kc[li], io.pos_dev, a->S, io.err_dev, (int)cdiv(n_kv_cap, PA_DS_KEYS), (float *)nullptr);
             PA_LAUNCH();
             pa_launch_dep(pdl, pa_k_dec_pv, dim3(cdiv(dv, PA_DP_DIMS), G, pa_dec_pv_split(H, G)), dim3(256), pa_dec_pv_smem(H, G), st, at, (const float *)a->S, (const float *)io.vct[li], io.pos_dev, a->att, pa_dec_pv_chunk(H, G), io.err_dev);
             PA_LAUNCH();

@@ -139,6 +139,7 @@ struct PaMv {
     float *kc, *vct;
     int n_ctx;
     const int32_t *pos;
+    int v_is_k;            // the K rows are the value rows as well: each goes to the K cache row AND to its V^T column (vd = 0)
     // extra fp32-input rows after the N weight rows: router logits z[e] = Wr[e] . h (h unrounded)
     const bf16 *Wr;
     int E;
@@ -210,10 +211,14 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_mv(const PaMv a) {
                 a.z[n - a.N] = v;
             } else {
                 if (a.bias) v += a.bias[n];
-                if (a.kd && n >= a.qd) {
+                if (a.kd && n >= a.qd && n < a.qd + a.kd + a.vd) {
                     const int p = a.pos[0];
-                    if (n < a.qd + a.kd) a.kc[(int64_t)p * a.kd + (n - a.qd)] = v;
-                    else a.vct[(int64_t)(n - a.qd - a.kd) * a.n_ctx + p] = v;
+                    if (n < a.qd + a.kd) {
+                        a.kc[(int64_t)p * a.kd + (n - a.qd)] = v;
+                        if (a.v_is_k) a.vct[(int64_t)(n - a.qd) * a.n_ctx + p] = v;
+                    } else {
+                        a.vct[(int64_t)(n - a.qd - a.kd) * a.n_ctx + p] = v;
+                    }
                 } else if (a.residual) {
                     a.residual[n] += v;
                 } else if (a.grp_rows > 0) {
@@ -232,8 +237,10 @@ __global__ void __launch_bounds__(PA_DV_THREADS) pa_k_dec_mv(const PaMv a) {
 // padded against bank conflicts) while the threads fetch q; then a thread per (key, head) forms the dot product with float4 reads
 // and applies scale / temperature / distance bias - no shuffles, and the bias look-ups of all pairs are in flight together.
 // CTAs from `tok_blocks` on take 16 pooled blocks each: the mean key rows behind the token rows, scores at pool_off, statistics at stat_off.
-__global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *__restrict__ q, const float *__restrict__ kc, const int32_t *__restrict__ pos_dev,
-                                                       float *__restrict__ b, int *__restrict__ err, int tok_blocks) {
+// With pool_v given, the last CTA also forms the means of the block that this token completes (no query sees that block before a
+// later step, so nothing in this launch reads them).
+__global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *__restrict__ q, const float *kc, const int32_t *__restrict__ pos_dev,
+                                                       float *__restrict__ b, int *__restrict__ err, int tok_blocks, float *pool_v) {
     extern __shared__ __align__(16) float sm[];
     __shared__ __align__(8) uint64_t bar;
     const int H = at.H, G = at.G, dq = at.dq, rep = H / G, kd = G * dq, kds = ((kd + 3) & ~3) + 4;
@@ -246,6 +253,8 @@ __global__ void __launch_bounds__(256) pa_k_dec_scores(PaAttn at, const float *_
     ps_grid_dep_launch();
     ps_grid_dep_wait();
     const int pos = pos_dev[0];
+    if (pool_v && at.pool > 0 && blockIdx.x == gridDim.x - 1 && (pos + 1) % at.pool == 0 && pos + 1 <= at.n_ctx)
+        for (int c = tid; c < kd + G * at.dv; c += 256) pa_pool_block(const_cast<float *>(kc), pool_v, kd, G * at.dv, at.n_ctx, at.pool, at.n_pool, (pos + 1) / at.pool - 1, c);
     const bool pooled = (int)blockIdx.x >= tok_blocks;
     int lo = pa_first_key(at, pos);
     int blk = lo / PA_DS_KEYS + blockIdx.x, j0 = blk * PA_DS_KEYS; // the grid starts at the block of the first key in sight

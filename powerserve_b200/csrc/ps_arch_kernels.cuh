@@ -160,23 +160,27 @@ __global__ void __launch_bounds__(256) pa_k_kv_store(const float *__restrict__ q
     else if (c < kd + vd) vct[(int64_t)(c - kd) * n_ctx + p] = row[v_off + c - kd];
 }
 
-// The means of the blocks of `pool` positions that the batch completes (block b ends at position b pool + pool - 1): K row n_ctx + b
-// and column b of the pooled V^T rows, each the sum of the block's cached entries in position order times 1 / pool - so a mean does
-// not depend on how the prompt was cut.  Grid (channels / 256, candidate blocks); the batch's first position comes from device memory.
-__global__ void __launch_bounds__(256) pa_k_pool_blocks(float *__restrict__ kc, float *__restrict__ vct, int kd, int vd, int n_ctx, int pool, int n_pool,
-                                                        const int32_t *__restrict__ pos, int bs) {
-    const int p0 = pos[0], b = p0 / pool + blockIdx.y, c = blockIdx.x * 256 + threadIdx.x;
-    if ((int64_t)(b + 1) * pool > p0 + bs || (int64_t)(b + 1) * pool > n_ctx || c >= kd + vd) return;
+// The means of block b of `pool` positions: K row n_ctx + b and column b of the pooled V^T rows, each the sum of the block's cached
+// entries in position order, divided by pool - so a mean does not depend on how the prompt was cut.  Channel c of kd + vd.
+__device__ __forceinline__ void pa_pool_block(float *__restrict__ kc, float *__restrict__ vct, int kd, int vd, int n_ctx, int pool, int n_pool, int b, int c) {
     const int j0 = b * pool;
     float s = 0.f;
     if (c < kd) {
         for (int j = 0; j < pool; j++) s += kc[(int64_t)(j0 + j) * kd + c];
         kc[(int64_t)(n_ctx + b) * kd + c] = s / (float)pool;
-    } else {
+    } else if (c < kd + vd) {
         const float *vr = vct + (int64_t)(c - kd) * n_ctx + j0;
         for (int j = 0; j < pool; j++) s += vr[j];
         vct[(int64_t)vd * n_ctx + (int64_t)(c - kd) * n_pool + b] = s / (float)pool;
     }
+}
+// the blocks that a batch completes (block b ends at position b pool + pool - 1).  Grid (channels / 256, candidate blocks); the
+// batch's first position comes from device memory.
+__global__ void __launch_bounds__(256) pa_k_pool_blocks(float *__restrict__ kc, float *__restrict__ vct, int kd, int vd, int n_ctx, int pool, int n_pool,
+                                                        const int32_t *__restrict__ pos, int bs) {
+    const int p0 = pos[0], b = p0 / pool + blockIdx.y, c = blockIdx.x * 256 + threadIdx.x;
+    if ((int64_t)(b + 1) * pool > p0 + bs || (int64_t)(b + 1) * pool > n_ctx) return;
+    pa_pool_block(kc, vct, kd, vd, n_ctx, pool, n_pool, b, c);
 }
 
 // x += mixer + sum of the feed-forward slots (fixed order)
