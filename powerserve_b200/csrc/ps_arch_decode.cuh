@@ -9,12 +9,14 @@
 //                          sequential blocks: the seam in the prologue (the pending sublayer output joins the residual stream through
 //                          its group norm, the sum is group-normed for this product; CTA 0 stores the sum to the second residual buffer),
 //                          per-head products (a row reads its head's slice of the input)
-//   pa_k_dec_scores      scores of all heads for 16 keys per CTA (thread per key and head out of shared memory), distance bias (table or
-//                        logarithmic), head mixing, per-block soft-max statistics; with a window the grid starts at the first key in sight
+//   pa_k_dec_scores      scores of all heads for 16 keys per CTA (thread per key and head out of shared memory), distance bias (table,
+//                        logarithmic or linear), head mixing, per-block soft-max statistics; with a window the grid starts at the first
+//                        key in sight; pooled windows: further CTAs take 16 block means each, and the last CTA forms the mean of the
+//                        block that the token completes
 //   pa_k_dec_pv          soft-max statistics (+ sink logit) per head, weights staged once per CTA, P.V along contiguous V^T rows; many
 //                        heads over one kv head are split over blockIdx.z
 //   pa_k_dec_dense_up    seam in the prologue, gate | up rows of a dense feed-forward (or of a shared expert, then with the router's
-//                        logits as further rows), activation
+//                        logits as further rows), activation; without a gate a warp's pair is two neighbouring up rows
 //   pa_k_dec_expert_up   norm + top-k of the router scores in the prologue, gate | up rows of the chosen experts, activation
 //   pa_k_dec_expert_down down rows of the chosen experts summed over the slots + mixer output + residual
 #pragma once

@@ -2,8 +2,11 @@
 //
 // Tiled kernels (any batch width): one 64 x 64 x 16 fp32 tile core shared by the dense projections, the routed experts
 // (rows gathered per expert), the attention scores (B operand = K cache rows) and P.V (B operand = V^T cache rows).
-// Sequential blocks add one-CTA-per-token kernels around them: the seam between two sublayers (group norm of the output, residual
-// add, group norm of the sum), unit-RMS q / k with the value blend on the way into the cache, the latent attention's norms and rotations.
+// Sequential blocks add one-CTA-per-token kernels around them: the seam between two sublayers (group or layer norm of the output,
+// residual add, what a new pass of a looped model adds, norm of the sum), unit-RMS q / k with the value blend on the way into the cache,
+// the latent attention's norms and rotations (half-split or neighbouring pairs).  Pooled windows: pa_k_pool_blocks forms the mean key /
+// value of every block of positions that a batch completes; the scores / soft-max / P.V kernels take the blocks as further keys behind
+// the tokens.  pa_k_dense_up1 is the first half of a feed-forward without a gate.
 // The single-token kernels (bs == 1) live in ps_arch_decode.cuh.
 #pragma once
 

@@ -14,6 +14,8 @@
 //                        state-space recurrence (a_t = exp(-exp(A_log) dt_t), c_t = dt_t, dt = softplus(raw + bias)); fp32 state,
 //                        16 entries of a value column per lane in registers, tokens strictly in order (the result does not
 //                        depend on how a prompt was cut)
+//   pa_k_gate_gru        after an attention: the heads' outputs times their sigmoid gate, and the minGRU beside the attention
+//                        (S_t = (1 - z) S_(t-1) + z cand per channel, rounds of 32 tokens, gates formed ahead of the dependent steps)
 //   pa_k_gate_norm       RMS norm in equal parts around a silu gate: (y silu(g)) normed times w, or normed y times silu(g)
 //   pa_k_moe_sum         sum of a token's expert slots (fixed order) plus the gated shared expert
 #pragma once
